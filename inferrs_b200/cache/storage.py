@@ -4,7 +4,7 @@ The reference allocates, per layer, K and V tensors ``[blocks * block_size,
 kv_heads, head_dim]`` (inferrs-models/src/kv_cache.rs:249-270).  Here one
 tensor per group holds all its caches,
 
-    [caches in group, 2 (keys, values), pages, kv_heads, page_size, head_dim]
+    [caches in group, 2 (keys, values; 1 for a cache of latents), pages, kv_heads, page_size, head_dim]
 
 so that one page of one head is a contiguous ``[page_size, head_dim]`` tile.
 Writes are plain stores; a page that is used again needs no clearing because a
@@ -27,6 +27,8 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    # 2: keys and values each have their pages; 1: one vector per token serves as both (a cache of latents)
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -61,12 +63,14 @@ class CacheStorage:
             members[g].append(cid)
         self.needs = keys
         self.members = members
+        if any(k.planes not in (1, 2) for k in keys):
+            raise ValueError("a cache has one plane (latents) or two (keys and values)")
         self.layouts = [GroupLayout(name=f"group{g}(heads={k.n_kv_heads},dim={k.head_dim},window={k.window})",
                                     window=k.window) for g, k in enumerate(keys)]
         self.n_pages = list(n_pages_per_group) if n_pages_per_group is not None else [n_pages] * len(keys)
         self.kv: List[torch.Tensor] = []
         for g, k in enumerate(keys):
-            self.kv.append(torch.zeros((len(members[g]), 2, self.n_pages[g], k.n_kv_heads, page_size, k.head_dim),
+            self.kv.append(torch.zeros((len(members[g]), k.planes, self.n_pages[g], k.n_kv_heads, page_size, k.head_dim),
                                        dtype=dtype, device=device))
         # one slot more than there are requests: the requests that only pad a replayed step write their state there
         self.states: Dict[int, torch.Tensor] = {
@@ -74,10 +78,11 @@ class CacheStorage:
             for cid, need in state_needs.items()}
 
     def pages(self, cache_id: int) -> Tuple[torch.Tensor, torch.Tensor, int]:
-        """(key pages, value pages, group index) of one cache; pages are [n_pages, kv_heads, page_size, head_dim]."""
+        """(key pages, value pages, group index) of one cache; pages are [n_pages, kv_heads, page_size, head_dim].
+        A cache of one plane gives the same pages twice."""
         g = self.group_of[cache_id]
         t = self.kv[g][self.index_in_group[cache_id]]
-        return t[0], t[1], g
+        return t[0], t[t.shape[0] - 1], g
 
     def state(self, cache_id: int) -> torch.Tensor:
         return self.states[cache_id]
@@ -98,7 +103,7 @@ class CacheStorage:
     def bytes_per_token(self) -> int:
         """Bytes of keys and values that one token adds, over all groups."""
         e = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(self.members[g]) * k.n_kv_heads * k.head_dim * e for g, k in enumerate(self.needs))
+        return sum(k.planes * len(self.members[g]) * k.n_kv_heads * k.head_dim * e for g, k in enumerate(self.needs))
 
     def total_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv) + \

@@ -117,7 +117,9 @@ def resolve_architecture(raw: RawConfig) -> Architecture:
     exact match is asked for here, so that a new architecture whose name
     contains an old one is refused instead of being run as the old one.
     """
-    names = raw.get_list("architectures", []) or []
+    names = list(raw.get_list("architectures", []) or [])
+    if raw.has("architecture"):          # some designs name themselves in a single string
+        names.append(raw.get_str("architecture"))
     for n in names:
         if isinstance(n, str) and n in _ARCHITECTURES:
             return _ARCHITECTURES[n]

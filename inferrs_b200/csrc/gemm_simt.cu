@@ -14,7 +14,11 @@
 template <typename XT, typename WT, typename OT>
 __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(const XT* __restrict__ x, const WT* __restrict__ w,
                                                             OT* __restrict__ y, int n_rows, int n_out, int k_dim,
-                                                            long ldx, long ldw, long ldy) {
+                                                            long ldx, long ldw, long ldy, long bx, long bw, long by) {
+    // blockIdx.z numbers the products of a batch: operand b starts bx, bw, by elements after operand b - 1
+    x += (long)blockIdx.z * bx;
+    w += (long)blockIdx.z * bw;
+    y += (long)blockIdx.z * by;
     __shared__ float xs[GT_BK][GT_BM + 4];
     __shared__ float ws[GT_BK][GT_BN + 4];
     const int tid = threadIdx.x;
@@ -64,10 +68,10 @@ __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(const XT* __restrict_
 
 template <typename XT, typename WT, typename OT>
 static int launch_gemm(const void* x, const void* w, void* y, int n_rows, int n_out, int k_dim, long ldx, long ldw,
-                       long ldy, cudaStream_t stream) {
-    const dim3 grid((n_out + GT_BN - 1) / GT_BN, (n_rows + GT_BM - 1) / GT_BM);
+                       long ldy, cudaStream_t stream, int batch = 1, long bx = 0, long bw = 0, long by = 0) {
+    const dim3 grid((n_out + GT_BN - 1) / GT_BN, (n_rows + GT_BM - 1) / GT_BM, batch);
     gemm_tn_simt_kernel<XT, WT, OT><<<grid, 256, 0, stream>>>((const XT*)x, (const WT*)w, (OT*)y, n_rows, n_out,
-                                                             k_dim, ldx, ldw, ldy);
+                                                             k_dim, ldx, ldw, ldy, bx, bw, by);
     return ib_launch_status();
 }
 
@@ -79,6 +83,28 @@ IB_EXPORT int ib_gemm_tn_simt(const void* x, int x_is_f32, const void* w, int w_
 #define IB_GEMM_CASE(XF, WF, YF, XT, WT, OT)                              \
     if ((x_is_f32 != 0) == XF && (w_is_f32 != 0) == WF && (y_is_f32 != 0) == YF) \
         return launch_gemm<XT, WT, OT>(x, w, y, n_rows, n_out, k_dim, ldx, ldw, ldy, stream);
+    IB_GEMM_CASE(true, true, true, float, float, float)
+#if IB_ACT_BF16
+    IB_GEMM_CASE(false, false, false, act_t, __nv_bfloat16, act_t)
+    IB_GEMM_CASE(false, false, true, act_t, __nv_bfloat16, float)
+    IB_GEMM_CASE(false, true, false, act_t, float, act_t)
+    IB_GEMM_CASE(false, true, true, act_t, float, float)
+    IB_GEMM_CASE(true, true, false, float, float, act_t)
+#endif
+#undef IB_GEMM_CASE
+    return IB_ERR_UNSUPPORTED;
+}
+
+// A batch of such products, y_b = x_b w_b^T for b < batch: operand b starts bx, bw, by elements after operand b - 1
+// (so the heads of one activation tensor, or of one weight tensor, are multiplied in place).
+IB_EXPORT int ib_gemm_tn_simt_batched(const void* x, int x_is_f32, const void* w, int w_is_f32, void* y, int y_is_f32,
+                                      int n_rows, int n_out, int k_dim, long ldx, long ldw, long ldy, int batch, long bx,
+                                      long bw, long by, cudaStream_t stream) {
+    if (n_rows <= 0 || n_out <= 0 || batch <= 0) return IB_OK;
+    if (k_dim <= 0 || batch > 65535) return IB_ERR_ARGUMENT;
+#define IB_GEMM_CASE(XF, WF, YF, XT, WT, OT)                              \
+    if ((x_is_f32 != 0) == XF && (w_is_f32 != 0) == WF && (y_is_f32 != 0) == YF) \
+        return launch_gemm<XT, WT, OT>(x, w, y, n_rows, n_out, k_dim, ldx, ldw, ldy, stream, batch, bx, bw, by);
     IB_GEMM_CASE(true, true, true, float, float, float)
 #if IB_ACT_BF16
     IB_GEMM_CASE(false, false, false, act_t, __nv_bfloat16, act_t)

@@ -13,22 +13,26 @@ from .. import models  # noqa: F401  (registers the architectures)
 from ..config.base import RawConfig, resolve_architecture
 from ..parts.spec import ModelSpec
 from ..runtime import Runtime
-from ..weights.loader import load_weights
+from ..weights.loader import load_weights, tensor_shapes
 from ..weights.random_init import random_weights
 from .model import declared_tensors
 
 
-def spec_from_config(config) -> Tuple[ModelSpec, object]:
-    """(model description, typed configuration) from a config.json path, folder or dict."""
+def spec_from_config(config, tensor_shapes=None) -> Tuple[ModelSpec, object]:
+    """(model description, typed configuration) from a config.json path, folder or dict.  ``tensor_shapes`` (name ->
+    shape, from the weight files' headers) goes to a configuration that takes sizes from there
+    (``with_tensor_shapes``)."""
     raw = config if isinstance(config, RawConfig) else (
         RawConfig(config, "<dict>") if isinstance(config, dict) else RawConfig.from_file(config))
     arch = resolve_architecture(raw)
     cfg = arch.config_cls.from_raw(raw)
+    if tensor_shapes is not None and hasattr(cfg, "with_tensor_shapes"):
+        cfg = cfg.with_tensor_shapes(tensor_shapes)
     return arch.build_spec(cfg), cfg
 
 
 def load_model_dir(model_dir: str, rt: Runtime) -> Tuple[ModelSpec, Dict[str, torch.Tensor], object]:
-    spec, cfg = spec_from_config(model_dir)
+    spec, cfg = spec_from_config(model_dir, tensor_shapes(model_dir))
     weights = load_weights(model_dir, declared_tensors(spec), rt.dtype, rt.device)
     return spec, weights, cfg
 

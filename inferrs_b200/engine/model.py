@@ -36,6 +36,9 @@ def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
             decls += part_class(sub.category, sub.part).declare(sub.part)
             if sub.post_norm is not None:
                 decls += part_class("norm", sub.post_norm).declare(sub.post_norm)
+        decls += _arrangement_tensors(layer)
+    if spec.position_table is not None:
+        decls.append(TensorDecl(spec.position_table, (spec.max_positions, spec.width)))
     decls += part_class("norm", spec.final_norm).declare(spec.final_norm)
     decls.append(TensorDecl(spec.lm_head, (spec.vocab_size, spec.width), optional=spec.lm_head_optional))
     seen, out = {}, []
@@ -47,6 +50,12 @@ def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
         seen[d.name] = d
         out.append(d)
     return out
+
+
+def _arrangement_tensors(layer) -> List[TensorDecl]:
+    """Tensors that belong to the way a layer's sub-layers hang on the residual (an arrangement with ``declare``)."""
+    cls = part_class("arrangement", _Arrangement(layer.arrangement))
+    return list(cls.declare(layer)) if hasattr(cls, "declare") else []
 
 
 def _check_category(category: str):
@@ -111,6 +120,7 @@ def _layer_tensor_names(layer) -> List[str]:
         for kind, d in (("norm", sub.norm), (sub.category, sub.part), ("norm", sub.post_norm)):
             if d is not None:
                 names += [t.name for t in part_class(kind, d).declare(d)]
+    names += [t.name for t in _arrangement_tensors(layer)]
     return names
 
 
@@ -123,6 +133,9 @@ class Model:
         self.spec = spec
         self.rt = rt
         self.embedding = weights[spec.embedding]
+        self.position_table = weights[spec.position_table] if spec.position_table is not None else None
+        if spec.streams is not None and spec.streams < 1:
+            raise ModelError(f"a residual has at least one stream, got {spec.streams}")
         self.blocks = []
         last_use = {}
         if consume:
@@ -140,7 +153,11 @@ class Model:
                     if sub.post_norm is not None else None
                 built.append(BuiltSubLayer(sub.category, part_class(sub.category, sub.part)(sub.part, weights, rt),
                                            norm, post))
-            self.blocks.append(part_class("arrangement", _Arrangement(layer.arrangement))(layer, built))
+            arrangement = part_class("arrangement", _Arrangement(layer.arrangement))
+            if getattr(arrangement, "needs_weights", False):
+                self.blocks.append(arrangement(layer, built, weights, rt))
+            else:
+                self.blocks.append(arrangement(layer, built))
             if consume:
                 for name in _layer_tensor_names(layer):
                     if last_use[name] == i and name not in (spec.embedding, spec.lm_head):
@@ -158,9 +175,18 @@ class Model:
     def forward(self, ctx) -> torch.Tensor:
         """Run the step's rows through all scheduled layers; float32 logits [wanted rows, vocab]."""
         n = ctx.token_ids.shape[0]
-        residual = torch.empty((n, self.spec.width), dtype=torch.float32, device=self.rt.device)
-        kernels.embedding_gather(self.embedding, ctx.token_ids, residual, self.rt.dtype,
-                                 1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale)
+        scale = 1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale
+        if self.spec.streams is None and self.position_table is None:
+            residual = torch.empty((n, self.spec.width), dtype=torch.float32, device=self.rt.device)
+            kernels.embedding_gather(self.embedding, ctx.token_ids, residual, self.rt.dtype, scale)
+        else:
+            # a residual of several streams [rows, streams, width], each the embedding (plus the position's vector)
+            residual = torch.empty((n, self.spec.streams or 1, self.spec.width), dtype=torch.float32,
+                                   device=self.rt.device)
+            kernels.embedding_streams(self.embedding, ctx.token_ids, self.position_table, ctx.positions, residual,
+                                      self.rt.dtype, scale)
+            if self.spec.streams is None:
+                residual = residual.view(n, self.spec.width)
         pending = None
         schedule = self.spec.schedule
         for k, entry in enumerate(schedule):

@@ -31,7 +31,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time, each request's count rounded up to 64")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
-    ap.add_argument("--max-requests", type=int, default=8, help="most requests that are live at a time")
+    ap.add_argument("--max-requests", type=int, default=4, help="most requests that are live at a time (state slots)")
     args = ap.parse_args(argv)
     if args.max_tokens <= 0:
         ap.error("--max-tokens must be positive")

@@ -63,6 +63,22 @@ _SIGNATURES = {
     "ib_argmax": [c_void_p, c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
     "ib_penalties": [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p],
+    "ib_embedding_streams": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_float, c_int, c_void_p],
+    "ib_stream_add_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                           c_int, c_int, c_int, c_float, c_void_p],
+    "ib_head_norm_gate": [c_void_p, c_int, c_long, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int,
+                          c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ib_poly_norm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "ib_latent_norm_store": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                             c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p],
+    "ib_linear_scan": [c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_float, c_float,
+                       c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ib_latent_attention": [c_void_p, c_int, c_long, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_long, c_long, c_void_p, c_void_p,
+                            c_void_p],
+    "ib_gemm_tn_simt_batched": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
+                                c_long, c_int, c_long, c_long, c_long, c_void_p],
     "ib_sample": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_int, c_void_p, c_void_p],
 }
@@ -163,6 +179,234 @@ def embedding_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, 
         raise KernelError(f"embedding_gather: ids {tuple(ids.shape)}, table {tuple(table.shape)}, out {tuple(out.shape)}")
     _check(_core(act_dtype).ib_embedding_gather(_p(table), int(table.dtype == torch.float32), _p(ids), _p(out), n,
                                                 width, table.shape[0], float(scale), _stream()), "embedding_gather")
+
+
+def embedding_streams(table: torch.Tensor, ids: torch.Tensor, pos_table: Optional[torch.Tensor],
+                      positions: Optional[torch.Tensor], out: torch.Tensor, act_dtype: torch.dtype, scale: float = 1.0):
+    """out[r, s, :] = table[ids[r]] * scale + pos_table[positions[r]] for every stream s, in float32
+    (``pos_table`` None: no learned positions).  ``out`` is [rows, streams, width]."""
+    _need(table, "table", _W, 2)
+    _need(ids, "ids", _I, 1)
+    _need(out, "out", (torch.float32,), 3)
+    _need(pos_table, "pos_table", _W, 2, optional=True)
+    n, streams, width = out.shape
+    if table.shape[1] != width or ids.shape[0] != n:
+        raise KernelError(f"embedding: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}")
+    if pos_table is not None:
+        _need(positions, "positions", _I, 1)
+        if pos_table.shape[1] != width or positions.shape[0] != n:
+            raise KernelError(f"embedding: position table {tuple(pos_table.shape)} for rows of width {width}")
+    _check(_core(act_dtype).ib_embedding_streams(
+        _p(table), int(table.dtype == torch.float32), _p(ids), _p(pos_table),
+        int(pos_table is not None and pos_table.dtype == torch.float32), _p(positions), _p(out), n, width,
+        table.shape[0], 0 if pos_table is None else pos_table.shape[0], float(scale), streams, _stream()),
+        "embedding_streams")
+
+
+def stream_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+                    gain: Optional[torch.Tensor], read: Optional[torch.Tensor], weight: torch.Tensor, groups: int,
+                    eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None):
+    """On a residual of several streams [rows, S, width] (float32, updated in place unless ``rows`` is given):
+    x_t <- sum_s mix[s, t] x_s + gain[t] * delta (``delta`` None: no update; ``mix`` None: the identity; ``gain``
+    None: ones), then u = sum_t read[t] x_t (``read`` None: the plain sum), then ``out`` = u with each of its
+    ``groups`` equal consecutive parts divided by its root mean square, times ``weight``."""
+    act = out.dtype
+    _need(residual, "residual", (torch.float32,), 3)
+    _need(delta, "delta", (act,), 2, optional=True)
+    _need(weight, "weight", _W, 1)
+    _need(out, "out", _W, 2)
+    _need(rows, "rows", _I, 1, optional=True)
+    n_src, streams, width = residual.shape
+    for name, t, size in (("mix", mix, streams * streams), ("gain", gain, streams), ("read", read, streams)):
+        _need(t, name, (torch.float32,), None, optional=True)
+        if t is not None and t.numel() != size:
+            raise KernelError(f"stream_add_norm: {name} has {t.numel()} numbers, {size} are needed for {streams} streams")
+    n = n_src if rows is None else rows.shape[0]
+    if out.shape != (n, width) or weight.shape[0] != width or (delta is not None and delta.shape != (n_src, width)):
+        raise KernelError(f"stream_add_norm: residual {tuple(residual.shape)}, out {tuple(out.shape)}, weight "
+                          f"{tuple(weight.shape)}, delta {None if delta is None else tuple(delta.shape)}")
+    if groups <= 0 or width % groups:
+        raise KernelError(f"stream_add_norm: a width of {width} cannot be cut into {groups} equal parts")
+    _check(_core(act).ib_stream_add_norm(
+        _p(residual), _p(delta), _p(mix), _p(gain), _p(read), _p(weight), int(weight.dtype == torch.float32), _p(out),
+        _p(rows), n, streams, width, int(groups), float(eps), _stream()), "stream_add_norm")
+
+
+GATE_SILU, GATE_SIGMOID = 0, 1
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], norm: bool, gate_act: int,
+                   eps: float, out: torch.Tensor):
+    """out[r, h*E + e] = o[r, h, e] / rms_h * weight * act(gate[r, h*E + e]) with rms_h = sqrt(mean_e(o[r, h]^2) + eps)
+    (``norm`` False: no division).  ``o`` is float32 or the activation dtype, [rows, H, E] or any view of that shape
+    whose last stride is 1 (a head-major result is read in place); ``gate`` is a [rows, H*E] view of a wider
+    projection; ``weight`` is None, [E] (shared by the heads) or [H*E]; ``gate_act`` is GATE_SILU or GATE_SIGMOID."""
+    act = out.dtype
+    if not (o.is_cuda and o.dim() == 3 and o.stride(2) == 1 and o.dtype in (torch.float32, act)):
+        raise KernelError(f"head_norm_gate: o must be a CUDA [rows, H, E] view with unit last stride in float32 or {act}")
+    n, heads, e_dim = o.shape
+    if not (gate.is_cuda and gate.dtype == act and gate.shape == (n, heads * e_dim) and gate.stride(1) == 1):
+        raise KernelError(f"head_norm_gate: gate must be a [rows, H*E] view in {act} with unit last stride")
+    _need(out, "out", _W, 2)
+    _need(weight, "weight", _W, 1, optional=True)
+    if out.shape != (n, heads * e_dim) or (weight is not None and weight.shape[0] not in (e_dim, heads * e_dim)):
+        raise KernelError(f"head_norm_gate: o {tuple(o.shape)}, out {tuple(out.shape)}, weight "
+                          f"{None if weight is None else tuple(weight.shape)}")
+    per_head = int(weight is not None and weight.shape[0] == heads * e_dim and heads > 1)
+    _check(_core(act).ib_head_norm_gate(
+        _p(o), int(o.dtype == torch.float32), o.stride(0), o.stride(1), _p(gate), gate.stride(0), _p(weight),
+        int(weight is not None and weight.dtype == torch.float32), per_head, int(bool(norm)), int(gate_act), float(eps),
+        _p(out), n, heads, e_dim, _stream()), "head_norm_gate")
+
+
+def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor):
+    """out = a z / r1 + b z^2 / r2 + c z^3 / r3 + e per row, r_p = sqrt(mean((z^p)^2) + eps), coef = (a, b, c, e) in
+    float32; powers element by element."""
+    act = out.dtype
+    _need(z, "z", (act,), 2)
+    _need(out, "out", _W, 2)
+    _need(coef, "coef", (torch.float32,), 1)
+    if out.shape != z.shape or coef.shape[0] != 4:
+        raise KernelError(f"poly_norm: z {tuple(z.shape)}, out {tuple(out.shape)}, coef {tuple(coef.shape)}")
+    _check(_core(act).ib_poly_norm(_p(z), _p(coef), _p(out), z.shape[0], z.shape[1], float(eps), _stream()), "poly_norm")
+
+
+def latent_norm_store(proj: torch.Tensor, q_col: int, q_weight: torch.Tensor, cq: torch.Tensor, kv_col: int,
+                      kv_weight: Optional[torch.Tensor], plane: Optional[torch.Tensor],
+                      block_table: Optional[torch.Tensor], row_request: torch.Tensor, positions: torch.Tensor,
+                      eps: float):
+    """Two slices of the rows of ``proj``, each divided by its root mean square and multiplied by its weight: columns
+    q_col.. (as many as ``q_weight`` has) go to ``cq``; columns kv_col.. (as many as ``kv_weight`` has) go to the
+    request's page of ``plane`` [pages, page_size, rank] at the row's position (``plane`` None: no second slice)."""
+    act = cq.dtype
+    _need(proj, "proj", (act,), 2)
+    _need(q_weight, "q_weight", _W, 1)
+    _need(cq, "cq", _W, 2)
+    n, ld = proj.shape
+    q_rank = q_weight.shape[0]
+    if cq.shape != (n, q_rank) or q_col < 0 or q_col + q_rank > ld:
+        raise KernelError(f"latent_norm_store: proj {tuple(proj.shape)}, cq {tuple(cq.shape)}, columns {q_col}..")
+    kv_rank, page_size, n_pages, max_pages = 0, 0, 0, 0
+    if plane is not None:
+        _need(plane, "plane", (act,), 3)
+        _need(kv_weight, "kv_weight", (q_weight.dtype,), 1)
+        _need(block_table, "block_table", _I, 2)
+        _need(row_request, "row_request", _I, 1)
+        _need(positions, "positions", _I, 1)
+        n_pages, page_size, kv_rank = plane.shape
+        max_pages = block_table.shape[1]
+        if kv_weight.shape[0] != kv_rank or kv_col < 0 or kv_col + kv_rank > ld:
+            raise KernelError(f"latent_norm_store: plane {tuple(plane.shape)}, weight {tuple(kv_weight.shape)}")
+    _check(_core(act).ib_latent_norm_store(
+        _p(proj), ld, q_col, q_rank, _p(q_weight), _p(cq), kv_col, kv_rank, _p(kv_weight),
+        int(q_weight.dtype == torch.float32), _p(plane), _p(block_table), max_pages, page_size, n_pages,
+        _p(row_request), _p(positions), n, float(eps), _stream()), "latent_norm_store")
+
+
+SCAN_CHANNEL_DECAY, SCAN_SCALAR_GATES = 0, 1
+
+
+def linear_scan(mode: int, proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gates: torch.Tensor,
+                gate_bias: torch.Tensor, gate_param: float, q_scale: float, state: torch.Tensor, q_start: torch.Tensor,
+                slots: torch.Tensor, n_requests: int, out: torch.Tensor, key_dim: int):
+    """A matrix state per head carried over each request's rows, one token after the other, in float32.
+
+    SCAN_CHANNEL_DECAY:  S = diag(sigmoid(z + b)^(1/gate_param)) S + k v^T,  o = S^T (q * q_scale)
+    SCAN_SCALAR_GATES:   i = c tanh((p + b_i)/c), f = logsigmoid(c tanh((r + b_f)/c)), c = gate_param,
+                         m' = max(f + m, i), S = exp(f + m - m') S + exp(i - m') k v^T (n likewise with k),
+                         o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+
+    ``proj`` [rows, ld] holds q and k as [H, D] and v as [H, E] from the given columns on; ``gates`` float32 holds z
+    [rows, H*D], or p and then r [rows, 2H]; ``out`` is float32 [rows, H, E]; ``state`` float32 [slots, ...] with at
+    least H*E*D (+ H*D + H) numbers per slot; request r's rows are q_start[r] .. q_start[r+1]-1, its slot slots[r]."""
+    act = proj.dtype
+    _need(proj, "proj", _W, 2)
+    _need(gates, "gates", (torch.float32,), 2)
+    _need(gate_bias, "gate_bias", (torch.float32,), 1)
+    _need(out, "out", (torch.float32,), 3)
+    _need(state, "state", (torch.float32,))
+    _need(q_start, "q_start", _I, 1)
+    _need(slots, "slots", _I, 1)
+    n, heads, e_dim = out.shape
+    d_dim = int(key_dim)
+    width = heads * d_dim if mode == SCAN_CHANNEL_DECAY else 2 * heads
+    if proj.shape[0] != n or gates.shape != (n, width) or gate_bias.shape[0] != width or d_dim <= 0 \
+            or max(q_col, k_col) + heads * d_dim > proj.shape[1] or v_col + heads * e_dim > proj.shape[1] \
+            or q_start.shape[0] < n_requests + 1 or slots.shape[0] < n_requests:
+        raise KernelError(f"linear_scan: proj {tuple(proj.shape)}, gates {tuple(gates.shape)}, out {tuple(out.shape)}")
+    if d_dim > 256:
+        raise KernelError(f"linear_scan: {d_dim} key channels per head are more than the kernel's 256")
+    slot_stride = state[0].numel()
+    _check(_core(act).ib_linear_scan(
+        int(mode), _p(proj), proj.shape[1], q_col, k_col, v_col, _p(gates), gates.shape[1], _p(gate_bias),
+        float(gate_param), float(q_scale), _p(state), slot_stride, _p(q_start), _p(slots), int(n_requests), _p(out),
+        heads, d_dim, e_dim, _stream()), "linear_scan")
+
+
+LATENT_SLICE_KEYS = 256     # keys per slice when a row's keys are cut over several blocks
+
+
+def latent_slices(n_rows: int, n_heads: int, max_kv_len: int) -> int:
+    """Into how many slices a row's keys are cut: one while the rows alone fill the machine, else so that about four
+    blocks per SM run, each slice with at least ``LATENT_SLICE_KEYS`` keys."""
+    blocks = n_rows * ((n_heads + 15) // 16)
+    if blocks >= 296:
+        return 1
+    by_length = max(1, (max_kv_len + LATENT_SLICE_KEYS - 1) // LATENT_SLICE_KEYS)
+    return max(1, min(by_length, (592 + blocks - 1) // blocks, 64))
+
+
+def latent_attention(q: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor, row_request: torch.Tensor,
+                     positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor, n_slices: int = 1):
+    """Attention of every row over its request's cached latents, which serve every head as key and as value:
+    out[h, r] = sum_j softmax_j(scale * q[h, r] . c_j) c_j over the visible j.  ``q`` and ``out`` are head-major
+    [H, rows, R] (float32 or the activation dtype; the activation dtype), ``plane`` [pages, page_size, R]."""
+    act = out.dtype
+    _need(q, "q", (torch.float32, act), 3)
+    _need(out, "out", _W, 3)
+    _need(plane, "plane", (act,), 3)
+    _need(block_table, "block_table", _I, 2)
+    _need(row_request, "row_request", _I, 1)
+    _need(positions, "positions", _I, 1)
+    heads, n, rank = q.shape
+    n_pages, page_size, r2 = plane.shape
+    if out.shape != q.shape or r2 != rank:
+        raise KernelError(f"latent_attention: q {tuple(q.shape)}, out {tuple(out.shape)}, plane {tuple(plane.shape)}")
+    if rank > 512:
+        raise KernelError(f"latent_attention: a latent of {rank} numbers is larger than the kernel's 512")
+    ws_acc = ws_ml = None
+    if n_slices > 1:
+        ws_acc = torch.empty((n * heads * n_slices, rank), dtype=torch.float32, device=q.device)
+        ws_ml = torch.empty((n * heads * n_slices, 2), dtype=torch.float32, device=q.device)
+    _check(_core(act).ib_latent_attention(
+        _p(q), int(q.dtype == torch.float32), rank, n * rank, _p(plane), _p(block_table), block_table.shape[1],
+        page_size, n_pages, _p(row_request), _p(positions), n, heads, rank, float(scale), int(window) if window else 0,
+        int(n_slices), _p(out), rank, n * rank, _p(ws_acc), _p(ws_ml), _stream()), "latent_attention")
+    if n_slices > 1:
+        count_launches(1)
+
+
+def batched_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_dtype: torch.dtype):
+    """out[b] = x[b] @ w[b].T for b < B: ``x`` [B, rows, K] (any view with unit last stride, so the heads of a
+    [rows, B*K] tensor are multiplied in place), ``w`` [B, M, K] and ``out`` [B, rows, M] contiguous.  True 32-bit
+    products with float32 activations or weights, else the tensor cores (the vendor's batched product)."""
+    if x.dim() != 3 or w.dim() != 3 or out.dim() != 3 or x.stride(2) != 1:
+        raise KernelError("batched_linear: x, w and out must have three dimensions, x with unit last stride")
+    _need(w, "w", _W, 3)
+    _need(out, "out", _W, 3)
+    b, n, k = x.shape
+    m = w.shape[1]
+    if w.shape != (b, m, k) or out.shape != (b, n, m) or not x.is_cuda:
+        raise KernelError(f"batched_linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if act_dtype == torch.float32 or w.dtype == torch.float32 or x.dtype == torch.float32:
+        code = _core(act_dtype).ib_gemm_tn_simt_batched(
+            _p(x), int(x.dtype == torch.float32), _p(w), int(w.dtype == torch.float32), _p(out),
+            int(out.dtype == torch.float32), n, m, k, x.stride(1), k, m, b, x.stride(0), m * k, n * m, _stream())
+        if code == -1:
+            raise KernelError(f"batched_linear: no kernel for x {x.dtype}, w {w.dtype}, out {out.dtype}")
+        _check(code, "gemm_tn_simt_batched")
+    else:
+        torch.bmm(x, w.transpose(1, 2), out=out)
 
 
 def resolve_tokens(ids: torch.Tensor, carry: torch.Tensor, act_dtype: torch.dtype):

@@ -11,9 +11,21 @@ from .registry import register_norm, register_position
 from .spec import NormSpec, PositionSpec, TensorDecl
 
 
+class StreamUpdate:
+    """A sub-layer's output that has not been brought into a residual of several streams yet:
+    x_t <- sum_s mix[s, t] x_s + gain[t] * delta.  The norm kernel that follows does it (``mix`` None: the identity;
+    ``gain`` None: ones).  ``mix`` and ``gain`` are float32 on the device."""
+
+    def __init__(self, delta: torch.Tensor, mix: Optional[torch.Tensor], gain: Optional[torch.Tensor]):
+        self.delta, self.mix, self.gain = delta, mix, gain
+
+
 class RMSNorm:
     """x / sqrt(mean(x^2) + eps) * w, in float32 (inferrs-kernels/candle-kernels/src/reduce.cu:188-228),
-    fused with the residual addition that precedes it in a block."""
+    fused with the residual addition that precedes it in a block.  With ``groups`` > 1 every one of that many equal
+    consecutive parts of the row is divided by its own root mean square.  On a residual of several streams
+    [rows, streams, width] the kernel also brings the pending output into the streams and reads their weighted
+    sum (``read``; None: the plain sum)."""
 
     graph_safe = True  # launches depend only on shapes, never on the step's host-side values
 
@@ -26,7 +38,17 @@ class RMSNorm:
         self.rt = rt
         self.weight = weights[spec.weight]
 
-    def add_norm(self, residual: torch.Tensor, delta, rows: Optional[torch.Tensor] = None):
+    def add_norm(self, residual: torch.Tensor, delta, rows: Optional[torch.Tensor] = None,
+                 read: Optional[torch.Tensor] = None):
+        groups = getattr(self.spec, "groups", 1)
+        if residual.dim() == 3 or groups != 1 or isinstance(delta, StreamUpdate) or read is not None:
+            streams = residual if residual.dim() == 3 else residual.unsqueeze(1)
+            update = delta if isinstance(delta, StreamUpdate) else StreamUpdate(delta, None, None)
+            n = streams.shape[0] if rows is None else rows.shape[0]
+            out = torch.empty((n, self.spec.size), dtype=self.rt.dtype, device=residual.device)
+            kernels.stream_add_norm(streams, update.delta, update.mix, update.gain, read, self.weight, groups,
+                                    self.spec.eps, out, rows)
+            return out
         if isinstance(delta, kernels.ScaledRows):
             # the product before has added its result to the residual stream and folded this norm in (it was given
             # this norm's sink): what it handed on stands for the norm's output
@@ -40,10 +62,14 @@ class RMSNorm:
 
     def sink(self, residual: torch.Tensor) -> "kernels.ResidualSink":
         """For a product that can fold the addition to the residual stream and this norm into its read-back."""
+        if getattr(self.spec, "groups", 1) != 1 or residual.dim() != 2:
+            raise ValueError("a norm in groups, or on a residual of several streams, is not folded into products")
         return kernels.ResidualSink(residual, self.weight, self.spec.eps)
 
     def norm(self, x: torch.Tensor) -> torch.Tensor:
         """The norm alone, on rows in the activation dtype (a norm on a sub-layer's output)."""
+        if getattr(self.spec, "groups", 1) != 1:
+            raise ValueError("a norm in groups has no form that stands after a sub-layer")
         out = torch.empty_like(x)
         kernels.rms_norm_rows(x, self.weight, self.spec.eps, out)
         return out

@@ -5,7 +5,9 @@ from typing import List, Optional
 
 import torch
 
+from .basic import StreamUpdate
 from .registry import register_arrangement
+from .spec import TensorDecl
 
 
 class BuiltSubLayer:
@@ -24,7 +26,8 @@ class BuiltSubLayer:
         """Whether this sub-layer can be handed scaled rows in place of its norm's output: the norm must be able to
         give a sink to the product before it, and the part must say that it reads scaled rows."""
         f = getattr(self.part, "takes_scaled_rows", None)
-        return f is not None and hasattr(self.norm, "sink") and bool(f(n_rows))
+        plain_norm = hasattr(self.norm, "sink") and getattr(getattr(self.norm, "spec", None), "groups", 1) == 1
+        return f is not None and plain_norm and bool(f(n_rows))
 
     def feeds_sink(self, n_rows: int) -> bool:
         f = getattr(self.part, "feeds_sink", None)
@@ -78,3 +81,63 @@ class SequentialBlock:
 
 
 register_arrangement("sequential", SequentialBlock)
+
+
+class HyperConnectionBlock:
+    """A block on a residual that is several streams wide, x_1 .. x_S [rows, S, width] in float32.  Every sub-layer has
+    a :class:`~inferrs_b200.parts.spec.StreamConnectionSpec`: it reads u = sum_s read[s] x_s through its norm, and
+    its output y comes back as x_t <- sum_s mix[s, t] x_s + gain[t] y, all streams at once from the old ones.
+
+    As in :class:`SequentialBlock` the output is not brought in where the sub-layer ends: the norm kernel that
+    follows does the update, the read and the norm in one pass over the streams, so the block hands its last
+    sub-layer's output on as a pending :class:`~inferrs_b200.parts.basic.StreamUpdate`.
+    """
+
+    needs_weights = True     # the model hands the arrangement the weights too: the connections' tensors
+
+    @staticmethod
+    def declare(spec) -> List[TensorDecl]:
+        out = []
+        for s in spec.sublayers:
+            c = s.connection
+            if c is None:
+                raise ValueError("every sub-layer of a hyper-connection block needs a connection")
+            out += [TensorDecl(c.read, (c.streams,), init=f"uniform:{1.0 / c.streams}:0.1"),
+                    TensorDecl(c.gain, (c.streams,), init="uniform:1:0.2"),
+                    TensorDecl(c.mix, (c.streams, c.streams), init="identity:0.1")]
+        return out
+
+    def __init__(self, spec, sublayers: List[BuiltSubLayer], weights=None, rt=None):
+        if not sublayers:
+            raise ValueError("a layer needs at least one sub-layer")
+        if weights is None:
+            raise ValueError("a hyper-connection block needs the weights of its connections")
+        self.spec = spec
+        self.sublayers = list(sublayers)
+        self.connections = []
+        for s, built in zip(spec.sublayers, sublayers):
+            c = s.connection
+            if c is None or not hasattr(built.norm, "add_norm") or built.post_norm is not None:
+                raise ValueError("a sub-layer of a hyper-connection block has a connection, a norm before it and none "
+                                 "after it")
+            self.connections.append(tuple(weights[name].to(torch.float32).contiguous() for name in (c.read, c.gain, c.mix)))
+        self.streams = spec.sublayers[0].connection.streams
+        if any(s.connection.streams != self.streams for s in spec.sublayers):
+            raise ValueError("the sub-layers of a block hang on the same number of streams")
+
+    def parts(self):
+        for s in self.sublayers:
+            yield s.part
+            yield s.norm
+
+    def forward(self, ctx, cache_id: int, residual: torch.Tensor, pending):
+        if residual.dim() != 3 or residual.shape[1] != self.streams:
+            raise ValueError(f"a hyper-connection block of {self.streams} streams got a residual of shape "
+                             f"{tuple(residual.shape)}")
+        for s, (read, gain, mix) in zip(self.sublayers, self.connections):
+            h = s.norm.add_norm(residual, pending, read=read)
+            pending = StreamUpdate(s.run(ctx, cache_id, h), mix, gain)
+        return pending
+
+
+register_arrangement("hyper_connections", HyperConnectionBlock)

@@ -9,7 +9,7 @@ from .. import kernels
 from ..runtime import Runtime
 from .basic import Linear, fuse_rows
 from .registry import register_feed_forward
-from .spec import GatedDenseSpec, TensorDecl
+from .spec import GatedDenseSpec, PolyNormDenseSpec, TensorDecl
 
 
 class GatedDense:
@@ -47,3 +47,33 @@ class GatedDense:
 
 
 register_feed_forward("gated_dense", GatedDense)
+
+
+class PolyNormDense:
+    """down( act(up(x)) ), act(z) = a U(z) + b U(z^2) + c U(z^3) + e with U the division of a row by its root mean
+    square: a polynomial activation whose three terms are brought to the same size before they are weighed.  The
+    sums of the three norms are float32; one kernel reads the up projection's rows once for all three."""
+
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec: PolyNormDenseSpec) -> List[TensorDecl]:
+        return [TensorDecl(spec.up_proj, (spec.inner, spec.width)),
+                TensorDecl(spec.down_proj, (spec.width, spec.inner)),
+                TensorDecl(spec.coef, (4,), init="uniform:0.4:0.3")]
+
+    def __init__(self, spec: PolyNormDenseSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        self.up = Linear(weights[spec.up_proj], rt)
+        self.down = Linear(weights[spec.down_proj], rt)
+        self.coef = weights[spec.coef].to(torch.float32).contiguous()
+
+    def forward(self, ctx, h):
+        z = self.up(h)
+        a = torch.empty_like(z)
+        kernels.poly_norm(z, self.coef, self.spec.eps, a)
+        return self.down(a)
+
+
+register_feed_forward("poly_norm_dense", PolyNormDense)

@@ -20,8 +20,9 @@ class TensorDecl:
     """One tensor that a part expects in the weight files.
 
     ``init`` tells the random-weights mode how to fill it: ``"normal"`` is
-    N(0, 0.02), ``"norm"`` is 1 + U(-0.1, 0.1).  ``optional`` tensors may be
-    absent; the part says what it does then.
+    N(0, 0.02), ``"norm"`` is 1 + U(-0.1, 0.1), ``"uniform:c:r"`` is c + U(-r, r),
+    ``"identity:r"`` (a square matrix) is the identity plus U(-r, r).  ``optional``
+    tensors may be absent; the part says what it does then.
     """
 
     name: str
@@ -32,10 +33,14 @@ class TensorDecl:
 
 @dataclass(frozen=True)
 class NormSpec:
+    """x / sqrt(mean(x^2) + eps) * weight.  ``groups`` > 1: the row is cut into that many equal consecutive parts
+    and each part is divided by its own root mean square."""
+
     size: int
     eps: float
     weight: str
     kind: str = "rms"
+    groups: int = 1
 
 
 @dataclass(frozen=True)
@@ -94,6 +99,116 @@ class GatedDenseSpec:
 
 
 @dataclass(frozen=True)
+class PolyNormDenseSpec:
+    """down( act(up(x)) ) with act(z) = a U(z) + b U(z^2) + c U(z^3) + e, powers element by element, U the division
+    of a row by its root mean square (``eps`` inside the root); ``coef`` names the tensor (a, b, c, e)."""
+
+    width: int
+    inner: int
+    up_proj: str
+    down_proj: str
+    coef: str
+    eps: float
+    kind: str = "poly_norm_dense"
+
+
+@dataclass(frozen=True)
+class ChannelDecayScanSpec:
+    """Gated linear attention: per head a matrix state S [key_dim, value_dim] with a decay per key channel,
+    S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t, q scaled by key_dim^(-1/2),
+    a_t = sigmoid(up(down(x)) + bias)^(1/tau).  Each head's o is divided by its root mean square and multiplied by
+    ``out_norm`` [value_dim] (one weight for all heads); the heads times silu(gate(x)) go through ``o_proj``."""
+
+    width: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    decay_rank: int
+    tau: float
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    o_proj: str
+    decay_down: str
+    decay_up: str
+    decay_bias: str
+    out_norm: str
+    kind: str = "channel_decay_scan"
+
+
+@dataclass(frozen=True)
+class ScalarGateScanSpec:
+    """The matrix memory of xLSTM: per head a state S [key_dim, value_dim], a vector n and a running maximum m, moved
+    by a log input gate i = cap tanh((W_i x + b_i) / cap) and a log forget gate f = logsigmoid(cap tanh((W_f x + b_f) /
+    cap)): m' = max(f + m, i), S' = exp(f + m - m') S + exp(i - m') k v^T (n likewise), o = S'^T q / (max(|n' . q|,
+    exp(-m')) + 1e-6), q scaled by key_dim^(-1/2).  Each head's o is divided by its root mean square; the heads times
+    ``out_norm`` [n_heads * value_dim] times sigmoid(gate(x)) go through ``o_proj``."""
+
+    width: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    o_proj: str
+    i_proj: str
+    i_bias: str
+    f_proj: str
+    f_bias: str
+    out_norm: str
+    kind: str = "scalar_gate_scan"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are made per head from one cached latent per token, without positions.
+
+    c_q = rmsnorm(dq(x)), q = uq(c_q) [n_heads, key_dim]; c = rmsnorm(dkv(x)) [kv_rank] is what the cache holds;
+    k_h = uk_h c, v_h = uv_h c [value_dim]; scores (q . k) * scale over j <= i (``window``: i - window < j), softmax;
+    the heads times sigmoid(gate(x)) go through ``o_proj``.  ``own_kv=False``: the layer has no ``dkv`` and reads
+    the latents that another schedule entry writes."""
+
+    width: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    eps: float
+    dq_proj: str
+    dq_norm: str
+    uq_proj: str
+    uk_proj: str
+    uv_proj: str
+    gate_proj: str
+    o_proj: str
+    dkv_proj: Optional[str] = None
+    dkv_norm: Optional[str] = None
+    window: Optional[int] = None
+    own_kv: bool = True
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class StreamConnectionSpec:
+    """How a sub-layer hangs on a residual that is ``streams`` copies wide (hyper-connections): it reads
+    u = sum_s read[s] x_s, and its output y comes back as x_t <- sum_s mix[s, t] x_s + gain[t] y (all t at once from
+    the old streams).  The three fields name the tensors [streams], [streams], [streams, streams]."""
+
+    streams: int
+    read: str
+    gain: str
+    mix: str
+
+
+@dataclass(frozen=True)
 class SubLayerSpec:
     """One sub-layer of a block: a part with what stands before and after it.
 
@@ -107,6 +222,8 @@ class SubLayerSpec:
     category: str
     norm: Optional[Any] = None
     post_norm: Optional[Any] = None
+    # for arrangements whose sub-layers hang on the residual in a way of their own (StreamConnectionSpec)
+    connection: Optional[Any] = None
 
 
 @dataclass(frozen=True)
@@ -141,7 +258,8 @@ class LayerSpec:
         for s in self.sublayers:
             if s.category == category:
                 if seen == index:
-                    s = SubLayerSpec(part=part, category=category, norm=s.norm, post_norm=s.post_norm)
+                    s = SubLayerSpec(part=part, category=category, norm=s.norm, post_norm=s.post_norm,
+                                     connection=s.connection)
                 seen += 1
             subs.append(s)
         if seen <= index:
@@ -185,6 +303,11 @@ class ModelSpec:
     # logits are multiplied by logit_scale and then squashed to cap * tanh(x / cap) (None: neither)
     logit_scale: Optional[float] = None
     logit_softcap: Optional[float] = None
+    # a learned vector per position [max_positions, width] that is added to the embedding (None: no such table)
+    position_table: Optional[str] = None
+    # the residual is this many streams wide, [rows, streams, width], all equal to the embedding at the start and
+    # summed before the last norm (None: the plain residual [rows, width])
+    streams: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
     architecture: str = ""
     extra: Tuple[Tuple[str, Any], ...] = field(default_factory=tuple)

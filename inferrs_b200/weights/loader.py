@@ -64,6 +64,24 @@ def weight_files(model_dir: str) -> List[str]:
     return files
 
 
+def tensor_shapes(model_dir: str) -> Dict[str, tuple]:
+    """name -> shape of every tensor in the folder's weight files, from their headers alone ({} if there are no
+    files)."""
+    try:
+        paths = weight_files(model_dir)
+    except WeightError:
+        return {}
+    out: Dict[str, tuple] = {}
+    for p in paths:
+        f = SafetensorsFile(p)
+        try:
+            for name, ti in f.info.items():
+                out[name] = tuple(ti.shape)
+        finally:
+            f.close()
+    return out
+
+
 def convert_for(t: torch.Tensor, stored: str, dtype: torch.dtype) -> torch.Tensor:
     """Apply the precision rule of this module to one tensor."""
     if stored in _INTS:

@@ -92,10 +92,28 @@ def _fill(out: torch.Tensor, key: int, init: str):
 def random_tensor(decl: TensorDecl, index: int, seed: int, dtype: torch.dtype,
                   device: torch.device = torch.device("cpu")) -> torch.Tensor:
     """``index`` (the tensor's place in the declaration) plays no part: the name does."""
-    if decl.init not in ("normal", "norm"):
-        raise ValueError(f"tensor '{decl.name}': unknown init '{decl.init}'")
+    kind, _, args = decl.init.partition(":")
     t = torch.empty(decl.shape, dtype=torch.float32, device=device)
-    _fill(t, _tensor_key(seed, decl.name), decl.init)
+    if kind in ("normal", "norm") and not args:
+        _fill(t, _tensor_key(seed, decl.name), kind)
+        return t.to(dtype)
+    # "uniform:c:r" = c + U(-r, r); "identity:r" = the identity plus U(-r, r): the same 24-bit uniform numbers that
+    # "norm" uses, moved and stretched
+    try:
+        numbers = [float(a) for a in args.split(":")] if args else []
+    except ValueError:
+        numbers = None
+    if kind == "uniform" and numbers is not None and len(numbers) == 2:
+        centre, spread = numbers
+    elif kind == "identity" and numbers is not None and len(numbers) == 1 and len(decl.shape) == 2 \
+            and decl.shape[0] == decl.shape[1]:
+        centre, spread = 0.0, numbers[0]
+    else:
+        raise ValueError(f"tensor '{decl.name}': unknown init '{decl.init}'")
+    _fill(t, _tensor_key(seed, decl.name), "norm")
+    t = (t - 1.0) * (spread / NORM_SPREAD) + centre
+    if kind == "identity":
+        t = t + torch.eye(decl.shape[0], dtype=torch.float32, device=device)
     return t.to(dtype)
 
 
