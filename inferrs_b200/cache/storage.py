@@ -61,6 +61,11 @@ class CacheStorage:
             self.group_of[cid] = g
             self.index_in_group[cid] = len(members[g])
             members[g].append(cid)
+        if not keys:
+            # a model whose mixers all keep fixed-size state: one group without caches still counts every request's
+            # tokens page by page (positions, the longest context), and holds no memory
+            keys.append(KVNeed(n_kv_heads=0, head_dim=0))
+            members.append([])
         self.needs = keys
         self.members = members
         if any(k.planes not in (1, 2) for k in keys):

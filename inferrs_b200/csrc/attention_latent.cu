@@ -170,8 +170,10 @@ static int launch_latent(IbDeviceSet& set, const void* q, long q_row, long q_hea
                          const int* positions, int n_rows, int n_heads, int R, float scale, int window, int n_slices,
                          void* out, long o_row, long o_head, float* ws_acc, float* ws_ml, cudaStream_t stream) {
     const size_t smem = ((size_t)LA_KEYS * (R + 1) + (size_t)LA_HEADS * R) * sizeof(float);
-    if (smem > 48 * 1024) {
-        const int e = ib_allow_dynamic_smem(set, latent_attention_kernel<QT, RPL>, smem);
+    // the most that this form of the kernel can ask for: the permission is given once per device
+    const size_t smem_most = ((size_t)LA_KEYS * (32 * RPL + 1) + (size_t)LA_HEADS * 32 * RPL) * sizeof(float);
+    if (smem_most > 48 * 1024) {
+        const int e = ib_allow_dynamic_smem(set, latent_attention_kernel<QT, RPL>, smem_most);
         if (e != IB_OK) return e;
     }
     const dim3 grid(n_rows, (n_heads + LA_HEADS - 1) / LA_HEADS, n_slices);

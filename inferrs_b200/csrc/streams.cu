@@ -139,18 +139,19 @@ IB_EXPORT int ib_stream_add_norm(float* residual, const void* delta, const float
     if (width <= 0 || streams <= 0 || groups <= 0 || width % groups || weight == nullptr) return IB_ERR_ARGUMENT;
     if (streams > IB_MAX_STREAMS || groups > IB_MAX_GROUPS) return IB_ERR_UNSUPPORTED;
     const size_t smem = (size_t)width * sizeof(float);
-    if (smem > 200 * 1024) return IB_ERR_UNSUPPORTED;
+    const size_t smem_most = 200 * 1024;      // the permission for more than 48 KB is given once per device, for the most
+    if (smem > smem_most) return IB_ERR_UNSUPPORTED;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (weight_is_f32) {
         if (smem > 48 * 1024) {
-            const int e = ib_allow_dynamic_smem(stream_norm_smem_f32, stream_add_norm_kernel<float>, smem);
+            const int e = ib_allow_dynamic_smem(stream_norm_smem_f32, stream_add_norm_kernel<float>, smem_most);
             if (e != IB_OK) return e;
         }
         ib_launch(stream_add_norm_kernel<float>, n_rows, threads, smem, stream, residual, (const act_t*)delta, mix, gain,
                   read, (const float*)weight, (act_t*)out, rows, streams, width, groups, eps);
     } else {
         if (smem > 48 * 1024) {
-            const int e = ib_allow_dynamic_smem(stream_norm_smem_bf16, stream_add_norm_kernel<__nv_bfloat16>, smem);
+            const int e = ib_allow_dynamic_smem(stream_norm_smem_bf16, stream_add_norm_kernel<__nv_bfloat16>, smem_most);
             if (e != IB_OK) return e;
         }
         ib_launch(stream_add_norm_kernel<__nv_bfloat16>, n_rows, threads, smem, stream, residual, (const act_t*)delta,

@@ -108,9 +108,11 @@ def latent_of(h, w, eps: float):
     return unit_rms(h @ w["dkv"].T, eps) * w["dkv.norm"]
 
 
-def latent_attention(h, c, w, heads: int, dim: int, vdim: int, scale: float, eps: float, start: int = 0):
+def latent_attention(h, c, w, heads: int, dim: int, vdim: int, scale: float, eps: float, start: int = 0,
+                     window: Optional[int] = None):
     """h [T, W]: the rows of positions start .. start+T-1;  c [start+T, R]: the latents of positions 0 .. start+T-1.
-    Keys and values are made from the latents per head; position i sees every j <= i; plain softmax."""
+    Keys and values are made from the latents per head; position i sees every j <= i (with a window: i - window < j);
+    plain softmax."""
     T = h.shape[0]
     cq = unit_rms(h @ w["dq"].T, eps) * w["dq.norm"]
     q = (cq @ w["uq"].T).reshape(T, heads, dim)
@@ -120,6 +122,8 @@ def latent_attention(h, c, w, heads: int, dim: int, vdim: int, scale: float, eps
     i = torch.arange(start, start + T)[:, None]
     j = torch.arange(c.shape[0])[None, :]
     score = score.masked_fill(j > i, float("-inf"))
+    if window is not None:
+        score = score.masked_fill(j <= i - window, float("-inf"))
     p = torch.softmax(score, dim=-1)
     o = torch.einsum("htj,jhe->the", p, v).reshape(T, heads * vdim)
     return (o * torch.sigmoid(h @ w["g"].T)) @ w["o"].T
@@ -135,7 +139,8 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
     streams after every layer."""
     wt = {k: v.to(dtype) for k, v in weights.items()}
     eps, groups = float(config["norm"]["eps"]), int(config["norm"]["groups"])
-    streams = int(config.get("streams", 1))
+    hyper = config.get("streams") is not None          # without the key: the plain residual x <- x + y
+    streams = int(config["streams"]) if hyper else 1
     T = len(tokens)
     x0 = wt["embed"][torch.tensor(tokens)] + wt["pos"][:T]
     xs = [x0.clone() for _ in range(streams)]
@@ -166,6 +171,9 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
         for q, (fn, present) in enumerate(((mixer, True), (ffn, layer.get("mlp") is not None)), start=1):
             if not present:
                 continue
+            if not hyper:
+                xs = [xs[0] + fn(grouped_norm(xs[0], wt[f"{p}norm{q}"], groups, eps))]
+                continue
             hc = sub(wt, f"{p}hc{q}.")
             u = sum(hc["in"][s] * xs[s] for s in range(streams))
             y = fn(grouped_norm(u, wt[f"{p}norm{q}"], groups, eps))
@@ -174,3 +182,13 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
             layer_sums.append(sum(xs))
     x = sum(xs)
     return grouped_norm(x, wt["final.norm"], groups, eps) @ wt["head"].T
+
+
+def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt: List[int], n_new: int, dtype=torch.float32) -> List[int]:
+    """The tokens that always taking the largest logit gives (the whole sequence is run again for every token)."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(torch.argmax(forward(config, weights, toks, dtype)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
