@@ -12,149 +12,193 @@
 // builds; q, k and v come from a projection in act_t.  A request's rows are walked in order, one token after the
 // other, so a result does not depend on how the prompt was cut into steps or on what else the step holds.
 //
-// Work split: a warp owns four columns of S for one (request, head); lane l owns the rows l, l + 32, ...  A token
-// costs the warp its q, k and gate loads (fetched one token ahead), D * 4 / 32 multiply-adds per lane for the update
-// and as many for the product with q, and one warp sum per column.  The warps of a block own neighbouring columns
-// of the same head, so q, k and the gates are fetched from L1 after the first warp.
+// Work split: a block owns 32 columns of S for one (request, head); lane l owns column l, warp w the rows 32 w ..
+// 32 w + 31, each lane's 32 numbers of S in registers.  Tokens go in chunks of 16: the block fetches the chunk's q, k,
+// v and gates together, a chunk ahead (one trip to memory per chunk, under the walk of the chunk before), turns the gates into
+// decays there with all threads (the exponentials, logarithms and hyperbolic tangents leave the sequential part;
+// of the running maximum only a chain of additions and comparisons stays sequential), then every warp walks the
+// chunk's tokens: per token 32 multiply-adds per lane for the update and 32 for the product with q, all operands but
+// S and v read from shared memory as the same word for the whole warp.  The warps' partial products are summed
+// through shared memory once per chunk.  In mode 1 the vector n is kept a row per lane by every warp for its rows,
+// and n . q is a warp sum per token that does not stand in the way of the update.
 //
-// State of one slot, float: S as [H, E, D] (D contiguous, so a warp's loads and stores are whole lines), then for
+// State of one slot, float: S as [H, D, E] (E contiguous: a warp's loads and stores are whole lines), then for
 // mode 1 n as [H, D] and m as [H].
 #include "common.cuh"
 
-#define LS_WARPS 8
-#define LS_COLS 4
+#define LS_CHUNK 16
+#define LS_COLS 32
 
 __device__ __forceinline__ float ls_logsigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
-template <int MODE, int NK>
-__global__ void __launch_bounds__(32 * LS_WARPS)
-linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col, int v_col,
-                   const float* __restrict__ gates, long ld_gates, const float* __restrict__ gate_bias,
-                   float gate_param, float q_scale, float* __restrict__ state, long slot_stride,
-                   const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ out,
-                   int H, int D, int E) {
+template <int MODE>
+__global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col, int v_col,
+                                   const float* __restrict__ gates, long ld_gates, const float* __restrict__ gate_bias,
+                                   float gate_param, float q_scale, float* __restrict__ state, long slot_stride,
+                                   const int* __restrict__ q_start, const int* __restrict__ slots,
+                                   float* __restrict__ out, int H, int D, int E) {
+    extern __shared__ __align__(16) float smem[];
     ib_grid_dependency_sync();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int h = blockIdx.y, r = blockIdx.z;
-    const int e0 = (blockIdx.x * LS_WARPS + warp) * LS_COLS;
-    if (e0 >= E) return;                       // whole warps leave; only warp-level exchanges follow
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int Dp = n_warps * 32;                        // D rounded up: the rows beyond D hold zeros
+    const int h = blockIdx.y, r = blockIdx.z, e0 = blockIdx.x * LS_COLS, d0 = warp * 32;
     const int row0 = q_start[r], row1 = q_start[r + 1];
-    if (row1 <= row0) return;
+    if (row1 <= row0) return;                           // the whole block leaves
+    float* q_s = smem;                                  // [LS_CHUNK][Dp]
+    float* k_s = q_s + LS_CHUNK * Dp;                   // [LS_CHUNK][Dp]   (mode 1: already times exp(i - m))
+    float* a_s = k_s + LS_CHUNK * Dp;                   // [LS_CHUNK][Dp]   mode 0: the decays
+    float* v_s = a_s + (MODE == 0 ? LS_CHUNK * Dp : 0); // [LS_CHUNK][32]
+    float* part = v_s + LS_CHUNK * LS_COLS;             // [LS_CHUNK][n_warps][32]
+    float* npart = part + LS_CHUNK * n_warps * LS_COLS; // [LS_CHUNK][n_warps]     mode 1
+    float* g_s = npart + LS_CHUNK * n_warps;            // [4][LS_CHUNK]           mode 1: i, f -> keep, take, exp(-m), m
+    float* m_s = g_s + 4 * LS_CHUNK;                    // [1]                     mode 1: the running maximum
+
     float* st = state + (long)slots[r] * slot_stride;
-    float* st_S = st + ((long)h * E + e0) * D;
-    float* st_n = st + (long)H * E * D + (long)h * D;
-    float* st_m = st + (long)H * E * D + (long)H * D + h;
+    float* st_S = st + (long)h * D * E;
+    float* st_n = st + (long)H * D * E + (long)h * D;
+    float* st_m = st + (long)H * D * E + (long)H * D + h;
+    const bool col_ok = e0 + lane < E;
 
-    float S[NK][LS_COLS], nvec[NK];
-    float m = 0.0f;
+    // the state's loads carry no condition either (see the chunk's loads below): the address is brought inside
+    float S[32];
+    const int e_in = min(e0 + lane, E - 1);
 #pragma unroll
-    for (int k = 0; k < NK; ++k) {
-        const int d = lane + 32 * k;
+    for (int i = 0; i < 32; ++i) S[i] = st_S[(long)min(d0 + i, D - 1) * E + e_in];
 #pragma unroll
-        for (int c = 0; c < LS_COLS; ++c) S[k][c] = (d < D && e0 + c < E) ? st_S[(long)c * D + d] : 0.0f;
-        nvec[k] = (MODE == 1 && d < D) ? st_n[d] : 0.0f;
+    for (int i = 0; i < 32; ++i) S[i] = (col_ok && d0 + i < D) ? S[i] : 0.0f;
+    float n_row = 0.0f;                                 // mode 1: n of row d0 + lane
+    if (MODE == 1) {
+        if (d0 + lane < D) n_row = st_n[d0 + lane];
+        if (threadIdx.x == 0) *m_s = *st_m;
     }
-    if (MODE == 1) m = *st_m;
+    __syncthreads();
 
-    float bias[NK];
-    float b_i = 0.0f, b_f = 0.0f;
-    if (MODE == 0) {
+    // One chunk's inputs as every thread fetches them: thread d owns key channel d of all the chunk's tokens (the
+    // block has Dp threads), and a share of the chunk's values.  They are asked for a chunk ahead and wait in
+    // registers while the chunk before is walked, so a trip to memory is paid once and under cover.
+    const int d_mine = threadIdx.x;
+    const bool d_ok = d_mine < D;
+    // Every load is issued whatever the chunk's length and the thread's channel (the address is brought inside the
+    // request's rows and the head's channels; what does not count is dropped when the registers are used): loads
+    // under a condition are waited for one by one, loads without one are all under way together.  The numbers stay
+    // as they were stored (act_t) until they are used, so nothing waits for them before the chunk is walked.
+    act_t rq[LS_CHUNK], rk[LS_CHUNK], rv[LS_CHUNK];
+    float rg[LS_CHUNK], r_gi = 0.0f, r_gf = 0.0f;
+    const float my_bias = (MODE == 0 && d_ok) ? gate_bias[h * D + d_mine] : 0.0f;
+    const int d_in = d_ok ? d_mine : D - 1;
+    const int last_row = row1 - 1;
+    auto fetch = [&](int c0) {
 #pragma unroll
-        for (int k = 0; k < NK; ++k) {
-            const int d = lane + 32 * k;
-            bias[k] = d < D ? gate_bias[h * D + d] : 0.0f;
+        for (int t = 0; t < LS_CHUNK; ++t) {
+            const act_t* p = proj + (long)min(c0 + t, last_row) * ld;
+            rq[t] = p[q_col + h * D + d_in];
+            rk[t] = p[k_col + h * D + d_in];
+            if (MODE == 0) rg[t] = gates[(long)min(c0 + t, last_row) * ld_gates + h * D + d_in];
+            const int idx = threadIdx.x + t * blockDim.x;          // the values: [tokens][32 columns]
+            const int vt = min(idx >> 5, LS_CHUNK - 1), ve = min(e0 + (idx & 31), E - 1);
+            rv[t] = proj[(long)min(c0 + vt, last_row) * ld + v_col + h * E + ve];
         }
-    } else {
-        b_i = gate_bias[h];
-        b_f = gate_bias[H + h];
-    }
-
-    // one token's inputs, fetched a token ahead of their use
-    float nq[NK], nk[NK], ng[NK] = {}, nv[LS_COLS], ngi = 0.0f, ngf = 0.0f;
-    auto fetch = [&](int row) {
-        const act_t* p = proj + (long)row * ld;
-#pragma unroll
-        for (int k = 0; k < NK; ++k) {
-            const int d = lane + 32 * k;
-            const bool ok = d < D;
-            nq[k] = ok ? ib_to_float(p[q_col + h * D + d]) : 0.0f;
-            nk[k] = ok ? ib_to_float(p[k_col + h * D + d]) : 0.0f;
-            if (MODE == 0) ng[k] = ok ? gates[(long)row * ld_gates + h * D + d] : 0.0f;
-        }
-#pragma unroll
-        for (int c = 0; c < LS_COLS; ++c) nv[c] = (e0 + c < E) ? ib_to_float(p[v_col + h * E + e0 + c]) : 0.0f;
-        if (MODE == 1) {
-            ngi = gates[(long)row * ld_gates + h];
-            ngf = gates[(long)row * ld_gates + H + h];
+        if (MODE == 1 && warp == 0) {
+            const float* gp = gates + (long)min(c0 + lane, last_row) * ld_gates;
+            r_gi = gp[h];
+            r_gf = gp[H + h];
         }
     };
     fetch(row0);
-    for (int row = row0; row < row1; ++row) {
-        float q[NK], kk[NK], g[NK], v[LS_COLS];
-#pragma unroll
-        for (int k = 0; k < NK; ++k) { q[k] = nq[k] * q_scale; kk[k] = nk[k]; g[k] = ng[k]; }
-#pragma unroll
-        for (int c = 0; c < LS_COLS; ++c) v[c] = nv[c];
-        const float gi = ngi, gf = ngf;
-        if (row + 1 < row1) fetch(row + 1);
 
-        float o[LS_COLS];
+    for (int c0 = row0; c0 < row1; c0 += LS_CHUNK) {
+        const int nc = min(LS_CHUNK, row1 - c0);
+        // ---- the chunk's inputs from the registers to shared memory, gates turned into decays ---------------
 #pragma unroll
-        for (int c = 0; c < LS_COLS; ++c) o[c] = 0.0f;
-        float den = 1.0f;
-        if (MODE == 0) {
-#pragma unroll
-            for (int k = 0; k < NK; ++k) {
-                const float a = expf(ls_logsigmoid(g[k] + bias[k]) * gate_param);      // gate_param = 1 / tau
-#pragma unroll
-                for (int c = 0; c < LS_COLS; ++c) {
-                    S[k][c] = fmaf(a, S[k][c], kk[k] * v[c]);
-                    o[c] = fmaf(S[k][c], q[k], o[c]);
-                }
+        for (int t = 0; t < LS_CHUNK; ++t) {
+            if (t < nc) {
+                q_s[t * Dp + d_mine] = d_ok ? ib_to_float(rq[t]) * q_scale : 0.0f;
+                k_s[t * Dp + d_mine] = d_ok ? ib_to_float(rk[t]) : 0.0f;
+                if (MODE == 0)
+                    a_s[t * Dp + d_mine] = d_ok ? expf(ls_logsigmoid(rg[t] + my_bias) * gate_param) : 1.0f;   // 1 / tau
             }
-        } else {
+            const int idx = threadIdx.x + t * blockDim.x;
+            if (idx < nc * LS_COLS) v_s[idx] = (e0 + (idx & 31) < E) ? ib_to_float(rv[t]) : 0.0f;
+        }
+        if (MODE == 1 && warp == 0) {
             const float cap = gate_param;
-            const float li = cap * tanhf((gi + b_i) / cap);
-            const float lf = ls_logsigmoid(cap * tanhf((gf + b_f) / cap));
-            const float m_new = fmaxf(lf + m, li);
-            const float keep = expf(lf + m - m_new), take = expf(li - m_new);
-            m = m_new;
-            float nq_dot = 0.0f;
-#pragma unroll
-            for (int k = 0; k < NK; ++k) {
-                const float tk = take * kk[k];
-                nvec[k] = fmaf(keep, nvec[k], tk);
-                nq_dot = fmaf(nvec[k], q[k], nq_dot);
-#pragma unroll
-                for (int c = 0; c < LS_COLS; ++c) {
-                    S[k][c] = fmaf(keep, S[k][c], tk * v[c]);
-                    o[c] = fmaf(S[k][c], q[k], o[c]);
-                }
+            float li = 0.0f, lf = 0.0f;
+            if (lane < nc) {
+                li = cap * tanhf((r_gi + gate_bias[h]) / cap);
+                lf = ls_logsigmoid(cap * tanhf((r_gf + gate_bias[H + h]) / cap));
             }
-            nq_dot = ib_warp_sum(nq_dot);
-            den = fmaxf(fabsf(nq_dot), expf(-m)) + 1e-6f;
+            // the running maximum: the only chain over the chunk's tokens, additions and comparisons
+            float m_prev = *m_s, m_before = 0.0f, m_mine = 0.0f;
+            for (int t = 0; t < nc; ++t) {
+                const float lit = __shfl_sync(0xffffffffu, li, t), lft = __shfl_sync(0xffffffffu, lf, t);
+                const float m_new = fmaxf(lft + m_prev, lit);
+                if (lane == t) { m_before = m_prev; m_mine = m_new; }
+                m_prev = m_new;
+            }
+            __syncwarp();
+            if (lane < nc) {
+                g_s[lane] = expf(lf + m_before - m_mine);              // keep
+                g_s[LS_CHUNK + lane] = expf(li - m_mine);              // take
+                g_s[2 * LS_CHUNK + lane] = expf(-m_mine);
+            }
+            if (lane == 0) *m_s = m_prev;
         }
-#pragma unroll
-        for (int c = 0; c < LS_COLS; ++c) o[c] = ib_warp_sum(o[c]);
-        if (lane < LS_COLS && e0 + lane < E) {
-            float mine = o[0];
-#pragma unroll
-            for (int c = 1; c < LS_COLS; ++c) mine = lane == c ? o[c] : mine;
-            out[((long)row * H + h) * E + e0 + lane] = MODE == 1 ? mine / den : mine;
+        __syncthreads();
+        if (c0 + LS_CHUNK < row1) fetch(c0 + LS_CHUNK);
+        if (MODE == 1) {                                 // k times exp(i - m), once for all columns
+            for (int idx = threadIdx.x; idx < nc * Dp; idx += blockDim.x) k_s[idx] *= g_s[LS_CHUNK + idx / Dp];
+            __syncthreads();
         }
+        // ---- the tokens, one after the other ----------------------------------------------------------------
+        for (int t = 0; t < nc; ++t) {
+            const float vt = v_s[t * LS_COLS + lane];
+            const float4* q4 = reinterpret_cast<const float4*>(q_s + t * Dp + d0);
+            const float4* k4 = reinterpret_cast<const float4*>(k_s + t * Dp + d0);
+            const float4* a4 = reinterpret_cast<const float4*>(a_s + t * Dp + d0);
+            const float keep = MODE == 1 ? g_s[t] : 0.0f;
+            float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 q = q4[i], k = k4[i];
+                float4 a;
+                if (MODE == 0) a = a4[i]; else a = make_float4(keep, keep, keep, keep);
+                S[4 * i + 0] = fmaf(a.x, S[4 * i + 0], k.x * vt); acc0 = fmaf(S[4 * i + 0], q.x, acc0);
+                S[4 * i + 1] = fmaf(a.y, S[4 * i + 1], k.y * vt); acc1 = fmaf(S[4 * i + 1], q.y, acc1);
+                S[4 * i + 2] = fmaf(a.z, S[4 * i + 2], k.z * vt); acc2 = fmaf(S[4 * i + 2], q.z, acc2);
+                S[4 * i + 3] = fmaf(a.w, S[4 * i + 3], k.w * vt); acc3 = fmaf(S[4 * i + 3], q.w, acc3);
+            }
+            part[(t * n_warps + warp) * LS_COLS + lane] = (acc0 + acc1) + (acc2 + acc3);
+            if (MODE == 1) {
+                n_row = fmaf(keep, n_row, k_s[t * Dp + d0 + lane]);
+                const float nq = ib_warp_sum(n_row * q_s[t * Dp + d0 + lane]);
+                if (lane == 0) npart[t * n_warps + warp] = nq;
+            }
+        }
+        __syncthreads();
+        // ---- the warps' shares of every token's product, summed ---------------------------------------------
+        for (int idx = threadIdx.x; idx < nc * LS_COLS; idx += blockDim.x) {
+            const int t = idx >> 5, e = idx & 31;
+            float o = 0.0f;
+            for (int w = 0; w < n_warps; ++w) o += part[(t * n_warps + w) * LS_COLS + e];
+            if (MODE == 1) {
+                float nq = 0.0f;
+                for (int w = 0; w < n_warps; ++w) nq += npart[t * n_warps + w];
+                o /= fmaxf(fabsf(nq), g_s[2 * LS_CHUNK + t]) + 1e-6f;
+            }
+            if (e0 + e < E) out[((long)(c0 + t) * H + h) * E + e0 + e] = o;
+        }
+        __syncthreads();
     }
 #pragma unroll
-    for (int k = 0; k < NK; ++k) {
-        const int d = lane + 32 * k;
-        if (d < D) {
-#pragma unroll
-            for (int c = 0; c < LS_COLS; ++c)
-                if (e0 + c < E) st_S[(long)c * D + d] = S[k][c];
-            if (MODE == 1 && e0 == 0) st_n[d] = nvec[k];
-        }
+    for (int i = 0; i < 32; ++i)
+        if (col_ok && d0 + i < D) st_S[(long)(d0 + i) * E + e0 + lane] = S[i];
+    if (MODE == 1 && blockIdx.x == 0) {
+        if (d0 + lane < D) st_n[d0 + lane] = n_row;
+        if (threadIdx.x == 0) *st_m = *m_s;
     }
-    if (MODE == 1 && e0 == 0 && lane == 0) *st_m = m;
 }
+
+static IbDeviceSet scan_smem_set[2];
 
 // proj [rows, ld] act_t holds q and k as [H, D] and v as [H, E] from columns q_col, k_col, v_col on.
 // gates [rows, ld_gates] float: mode 0 the decay's pre-activations [H, D] (gate_bias [H * D], gate_param = tau);
@@ -171,18 +215,24 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
     if (D > 256 || H > 65535 || n_requests > 65535) return IB_ERR_UNSUPPORTED;
     const long need = (long)H * E * D + (mode == 1 ? (long)H * D + H : 0);
     if (slot_stride < need) return IB_ERR_ARGUMENT;
-    const dim3 grid((E + LS_WARPS * LS_COLS - 1) / (LS_WARPS * LS_COLS), H, n_requests);
+    const int n_warps = (D + 31) / 32;
+    const dim3 grid((E + LS_COLS - 1) / LS_COLS, H, n_requests);
     const float param = mode == 0 ? 1.0f / gate_param : gate_param;
-#define IB_SCAN(MODE, NK)                                                                                          \
-    ib_launch(linear_scan_kernel<MODE, NK>, grid, 32 * LS_WARPS, 0, stream, (const act_t*)proj, ld, q_col, k_col,  \
-              v_col, gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start, slots, out, H, D, E)
-#define IB_SCAN_NK(MODE)                                                                                           \
-    do {                                                                                                           \
-        if (D <= 32) IB_SCAN(MODE, 1); else if (D <= 64) IB_SCAN(MODE, 2);                                         \
-        else if (D <= 128) IB_SCAN(MODE, 4); else IB_SCAN(MODE, 8);                                                \
-    } while (0)
-    if (mode == 0) IB_SCAN_NK(0); else IB_SCAN_NK(1);
-#undef IB_SCAN_NK
-#undef IB_SCAN
+    auto smem_for = [](int warps) {
+        return (size_t)(3 * LS_CHUNK * warps * 32 + LS_CHUNK * LS_COLS + LS_CHUNK * warps * LS_COLS + LS_CHUNK * warps +
+                        4 * LS_CHUNK + 4) * sizeof(float);
+    };
+    const size_t smem = smem_for(n_warps);
+    if (smem > 48 * 1024) {   // the permission is given once per device, for the most that the kernel can ask for
+        const int e = mode == 0 ? ib_allow_dynamic_smem(scan_smem_set[0], linear_scan_kernel<0>, smem_for(8))
+                                : ib_allow_dynamic_smem(scan_smem_set[1], linear_scan_kernel<1>, smem_for(8));
+        if (e != IB_OK) return e;
+    }
+    if (mode == 0)
+        ib_launch(linear_scan_kernel<0>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld, q_col, k_col, v_col,
+                  gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start, slots, out, H, D, E);
+    else
+        ib_launch(linear_scan_kernel<1>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld, q_col, k_col, v_col,
+                  gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start, slots, out, H, D, E);
     return ib_launch_status();
 }

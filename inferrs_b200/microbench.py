@@ -139,6 +139,73 @@ def attention(args) -> dict:
                  "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}, **extra)
 
 
+def scan(args) -> dict:
+    """The scan kernel alone (a matrix state per head): one prompt of ``tokens`` rows, or ``batch`` requests of one
+    token each.  Bytes: the projection's q, k and v, the gates, the result, and every touched state read and
+    written once."""
+    h, d, e = args.heads, args.key_dim, args.value_dim
+    dev = torch.device("cuda")
+    dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
+    lens = [args.tokens] if args.form == "prefill" else [1] * args.batch
+    n = sum(lens)
+    ld = 2 * h * d + 2 * h * e
+    proj = torch.randn(n, ld, device=dev).to(dtype)
+    mode = kernels.SCAN_CHANNEL_DECAY if args.mode == "decay" else kernels.SCAN_SCALAR_GATES
+    gw = h * d if args.mode == "decay" else 2 * h
+    gates = torch.randn(n, gw, device=dev)
+    bias = torch.randn(gw, device=dev) + 3.0
+    n_state = h * e * d + (h * d + h if args.mode == "gates" else 0)
+    state = torch.zeros(len(lens) + 1, n_state, device=dev)
+    q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+    out = torch.empty(n, h, e, dtype=torch.float32, device=dev)
+    fn = lambda: kernels.linear_scan(mode, proj, 0, h * d, 2 * h * d, gates, bias, 8.0, d ** -0.5, state, q_start,  # noqa: E731
+                                     slots, len(lens), out, d)
+    us = _time(fn, args.iters)
+    el = 4 if dtype == torch.float32 else 2
+    byts = n * (2 * h * d + h * e) * el + n * gw * 4 + n * h * e * 4 + 2 * len(lens) * n_state * 4
+    flops = 4 * n * h * d * e
+    return {"kernel": f"scan/{args.mode}/{args.form}", "heads": h, "key_dim": d, "value_dim": e, "rows": n,
+            "requests": len(lens), "us": round(us, 2), "GBps": round(byts / us / 1e3, 1),
+            "TFLOPs": round(flops / us / 1e6, 2), "us_per_token": round(us / max(lens), 4)}
+
+
+def latent(args) -> dict:
+    """The attention over cached latents alone: one prompt of ``tokens`` rows after ``context_before`` cached ones, or
+    ``batch`` single tokens over ``context`` latents each.  Flops: scores and sums over the latents, 4 R per head,
+    row and visible key; bytes: every visible latent once per request, queries and results."""
+    h, r, ps = args.heads, args.rank, args.page_size
+    dev = torch.device("cuda")
+    dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
+    if args.form == "decode":
+        lens, new = [args.context] * args.batch, [1] * args.batch
+    else:
+        lens, new = [args.context_before + args.tokens], [args.tokens]
+    pages_per = [(n + ps - 1) // ps for n in lens]
+    n_pages = sum(pages_per)
+    table = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages).to(torch.int32)
+    at = 0
+    for i, n in enumerate(pages_per):
+        table[i, :n] = perm[at:at + n]
+        at += n
+    positions = torch.tensor([p for n, t in zip(lens, new) for p in range(n - t, n)], dtype=torch.int32, device=dev)
+    row_request = torch.tensor([i for i, t in enumerate(new) for _ in range(t)], dtype=torch.int32, device=dev)
+    n = sum(new)
+    q = torch.randn(h, n, r, device=dev).to(dtype)
+    plane = torch.randn(n_pages, ps, r, device=dev).to(dtype)
+    out = torch.empty(h, n, r, dtype=dtype, device=dev)
+    slices = args.slices or kernels.latent_slices(n, h, max(lens))
+    fn = lambda: kernels.latent_attention(q, plane, table.to(dev), row_request, positions, r ** -0.5, None, out, slices)  # noqa: E731
+    us = _time(fn, args.iters)
+    el = 4 if dtype == torch.float32 else 2
+    pairs = sum(t * (c - t) + t * (t + 1) // 2 for c, t in zip(lens, new))
+    byts = el * (sum(lens) * r + 2 * n * h * r)
+    flops = 4 * h * r * pairs
+    return {"kernel": f"latent_attention/{args.form}", "heads": h, "rank": r, "rows": n, "keys": lens[0],
+            "slices": slices, "us": round(us, 2), "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 2)}
+
+
 def chain(args) -> dict:
     """The four projections of `layers` decoder layers back to back in one CUDA graph, every layer with weights
     of its own: what a decode step pays for its matrix products, launch gaps and cold starts included."""
@@ -458,6 +525,30 @@ def main(argv=None) -> int:
     a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--iters", type=int, default=20)
     a.set_defaults(fn=attention)
+    sc = sub.add_parser("scan")
+    sc.add_argument("--mode", choices=["decay", "gates"], default="gates")
+    sc.add_argument("--form", choices=["decode", "prefill"], default="prefill")
+    sc.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
+    sc.add_argument("--batch", type=int, default=8)
+    sc.add_argument("--tokens", type=int, default=2048)
+    sc.add_argument("--heads", type=int, default=16)
+    sc.add_argument("--key-dim", type=int, default=128)
+    sc.add_argument("--value-dim", type=int, default=128)
+    sc.add_argument("--iters", type=int, default=20)
+    sc.set_defaults(fn=scan)
+    la = sub.add_parser("latent")
+    la.add_argument("--form", choices=["decode", "prefill"], default="prefill")
+    la.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
+    la.add_argument("--batch", type=int, default=8)
+    la.add_argument("--context", type=int, default=2048)
+    la.add_argument("--tokens", type=int, default=2048)
+    la.add_argument("--context-before", type=int, default=0)
+    la.add_argument("--heads", type=int, default=16)
+    la.add_argument("--rank", type=int, default=512)
+    la.add_argument("--slices", type=int, default=0, help="slices of a row's keys (0: as the engine chooses)")
+    la.add_argument("--page-size", type=int, default=16)
+    la.add_argument("--iters", type=int, default=20)
+    la.set_defaults(fn=latent)
     c = sub.add_parser("chain")
     c.add_argument("--impl", choices=["library", "tcgen05", "folded", "persistent"], default="library",
                    help="folded: the products with the norms folded in, one kernel each; persistent: the same four as one kernel")

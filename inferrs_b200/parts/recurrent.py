@@ -69,7 +69,7 @@ class ChannelDecayScan(_ScanMixer):
 
     @staticmethod
     def state_need(spec: ChannelDecayScanSpec) -> Optional[StateNeed]:
-        return StateNeed(shape=(spec.n_heads * spec.value_dim * spec.key_dim,))
+        return StateNeed(shape=(spec.n_heads * spec.key_dim * spec.value_dim,))
 
     def __init__(self, spec: ChannelDecayScanSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         if spec.tau <= 0:
@@ -104,7 +104,7 @@ class ScalarGateScan(_ScanMixer):
     @staticmethod
     def state_need(spec: ScalarGateScanSpec) -> Optional[StateNeed]:
         h, d, e = spec.n_heads, spec.key_dim, spec.value_dim
-        return StateNeed(shape=(h * e * d + h * d + h,))     # the matrices, the vectors n, the maxima m
+        return StateNeed(shape=(h * d * e + h * d + h,))     # the matrices, the vectors n, the maxima m
 
     def __init__(self, spec: ScalarGateScanSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         if spec.gate_cap <= 0:
