@@ -134,7 +134,9 @@ latent_attention_kernel(const QT* __restrict__ q, long q_row, long q_head, const
     }
 }
 
-// Joins the slices of one (row, head): a warp each, slices in ascending order.
+// Joins the slices of one (row, head): a warp each.  A lane owns up to two slices' weights exp(m_s - m) (at most 64
+// slices); the sums then run over the slices in ascending order with loads that carry no condition (a slice without
+// keys has left zeros and the weight 0), so they are all under way together.
 __global__ void latent_attention_join_kernel(const float* __restrict__ ws_acc, const float* __restrict__ ws_ml,
                                              int n_rows, int n_heads, int R, int n_slices, act_t* __restrict__ out,
                                              long o_row, long o_head) {
@@ -143,24 +145,285 @@ __global__ void latent_attention_join_kernel(const float* __restrict__ ws_acc, c
     const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= (long)n_rows * n_heads) return;
     const int row = (int)(item / n_heads), h = (int)(item % n_heads);
-    float m = -INFINITY;
-    for (int s = 0; s < n_slices; ++s) m = fmaxf(m, ws_ml[(item * n_slices + s) * 2]);
-    float l = 0.0f;
-    for (int s = 0; s < n_slices; ++s) {
-        const float ms = ws_ml[(item * n_slices + s) * 2];
-        if (ms != -INFINITY) l += ws_ml[(item * n_slices + s) * 2 + 1] * expf(ms - m);
+    const float* ml = ws_ml + item * n_slices * 2;
+    float ms[2], ls[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int s = min(lane + 32 * k, n_slices - 1);
+        ms[k] = ml[s * 2];
+        ls[k] = ml[s * 2 + 1];
+        if (lane + 32 * k >= n_slices) { ms[k] = -INFINITY; ls[k] = 0.0f; }
     }
+    const float m = ib_warp_max(fmaxf(ms[0], ms[1]));
+    float w[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) w[k] = (ms[k] == -INFINITY) ? 0.0f : expf(ms[k] - m);
+    const float l = ib_warp_sum(ls[0] * w[0] + ls[1] * w[1]);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    const float* acc = ws_acc + item * n_slices * R;
     act_t* dst = out + (long)row * o_row + (long)h * o_head;
-    for (int e = lane; e < R; e += 32) {
-        float v = 0.0f;
-        for (int s = 0; s < n_slices; ++s) {
-            const float ms = ws_ml[(item * n_slices + s) * 2];
-            if (ms != -INFINITY) v = fmaf(ws_acc[(item * n_slices + s) * R + e], expf(ms - m), v);
+    // all of a slice's numbers for this lane are asked for together (up to 16 loads under way), slice after slice
+    float v[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) v[k] = 0.0f;
+#pragma unroll 2
+    for (int s = 0; s < n_slices; ++s) {
+        const float ws = __shfl_sync(0xffffffffu, s < 32 ? w[0] : w[1], s & 31);
+        const float* a = acc + (long)s * R;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) v[k] = fmaf(a[min(lane + 32 * k, R - 1)], ws, v[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+        if (lane + 32 * k < R) dst[lane + 32 * k] = ib_from_float<act_t>(v[k] * inv);
+}
+
+#if IB_ACT_BF16
+// ---------------------------------------------------------------------------------------------------------------
+// The same on the tensor cores (bfloat16 build; latents of a multiple of 32 numbers).  A block owns one row's group
+// of up to 16 heads: the 16 x R queries are the A operand of both products.  Keys come 64 at a time by cp.async into
+// one buffer (the shared memory then leaves room for two blocks per SM, which cover each other's waits).  Scores: every one of the four warps takes
+// 16 of the 64 keys over the whole of R (mma.sync m16n8k16, float32 accumulation); the softmax's maxima and sums go
+// through shared memory, P as bfloat16 too.  Sums: every warp takes a quarter of R over all 64 keys, the latents
+// read as the B operand through a transposing ldmatrix, so each latent is fetched once for both products.
+// ---------------------------------------------------------------------------------------------------------------
+#define LM_KEYS 64
+#define LM_ROWS 16
+#define LM_PAD 8
+
+__device__ __forceinline__ void lm_ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void lm_ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void lm_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void lm_cp_async16(void* dst, const void* src, int src_bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+
+template <int NT>   // n-tiles of 8 columns per warp in the second product: R = 32 * NT
+__global__ void __launch_bounds__(128)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long q_row, long q_head,
+                            const __nv_bfloat16* __restrict__ plane, const int* __restrict__ block_table, int max_pages,
+                            int page_size, int n_pages, const int* __restrict__ row_request,
+                            const int* __restrict__ positions, int n_heads, float scale, int window, int n_slices,
+                            __nv_bfloat16* __restrict__ out, long o_row, long o_head, float* __restrict__ ws_acc,
+                            float* __restrict__ ws_ml) {
+    constexpr int R = 32 * NT, LDC = R + LM_PAD, LDP = LM_KEYS + LM_PAD;
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [16][LDC]
+    __nv_bfloat16* c_s = q_s + LM_ROWS * LDC;                                // [64][LDC]
+    __nv_bfloat16* p_s = c_s + LM_KEYS * LDC;                                // [16][LDP]
+    float* pmax = reinterpret_cast<float*>(p_s + LM_ROWS * LDP);             // [4][16]
+    float* psum = pmax + 4 * LM_ROWS;                                        // [4][16]
+    ib_grid_dependency_sync();
+    const int row = blockIdx.x, slice = blockIdx.z, head0 = blockIdx.y * LM_ROWS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[row];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int* bt = block_table + (long)row_request[row] * max_pages;
+    const int first = (lo / LM_KEYS) * LM_KEYS;
+    const int n_tiles = (pos - first) / LM_KEYS + 1;
+    const int per_slice = (n_tiles + n_slices - 1) / n_slices;
+    const int t0 = slice * per_slice, t1 = min(n_tiles, t0 + per_slice);
+
+    // the queries of the group's heads (rows of heads that do not exist are zeros)
+    for (int i = threadIdx.x; i < LM_ROWS * (R / 8); i += blockDim.x) {
+        const int m = i / (R / 8), ch = i % (R / 8);
+        const int h = head0 + m;
+        const __nv_bfloat16* src = q + (long)row * q_row + (long)min(h, n_heads - 1) * q_head + ch * 8;
+        lm_cp_async16(q_s + m * LDC + ch * 8, src, h < n_heads ? 16 : 0);
+    }
+    // two threads per key: the page is looked up once per key and tile, each thread copies half of the latent
+    auto load_tile = [&](int t) {
+        const int jj = threadIdx.x >> 1, half = threadIdx.x & 1;
+        const int j = first + t * LM_KEYS + jj;
+        const __nv_bfloat16* src = plane;
+        int bytes = 0;
+        if (j >= lo && j <= pos) {
+            const int page = bt[j / page_size];
+            if (page >= 0 && page < n_pages) {
+                src = plane + ((long)page * page_size + (j % page_size)) * R;
+                bytes = 16;
+            }
         }
-        dst[e] = ib_from_float<act_t>(v * inv);
+        __nv_bfloat16* dst = c_s + jj * LDC;
+#pragma unroll
+        for (int ch = half; ch < R / 8; ch += 2) lm_cp_async16(dst + ch * 8, bytes ? src + ch * 8 : src, bytes);
+    };
+    if (t0 < t1) load_tile(t0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};     // rows lane/4 and lane/4 + 8
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+
+    for (int t = t0; t < t1; ++t) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const __nv_bfloat16* ct = c_s;
+        // ---- scores of this warp's 16 keys ------------------------------------------------------------------
+        // (two sets of accumulators take turns, so that a product does not wait for the one before it)
+        float sc[2][4], sd[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+            sd[i][0] = sd[i][1] = sd[i][2] = sd[i][3] = 0.0f;
+        }
+#pragma unroll
+        for (int ks = 0; ks < R / 16; ++ks) {
+            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+            lm_ldmatrix_x4(a0, a1, a2, a3, q_s + (lane & 15) * LDC + ks * 16 + (lane >> 4) * 8);
+            lm_ldmatrix_x4(b0, b1, b2, b3, ct + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * LDC + ks * 16 + ((lane >> 3) & 1) * 8);
+            if (ks & 1) {
+                lm_mma(sd[0], a0, a1, a2, a3, b0, b1);
+                lm_mma(sd[1], a0, a1, a2, a3, b2, b3);
+            } else {
+                lm_mma(sc[0], a0, a1, a2, a3, b0, b1);
+                lm_mma(sc[1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) sc[i][c] += sd[i][c];
+        const int j_base = first + t * LM_KEYS + warp * 16 + 2 * (lane & 3);
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int j = j_base + i * 8 + (c & 1);
+                const float v = (j >= lo && j <= pos) ? sc[i][c] * scale : -INFINITY;
+                sc[i][c] = v;
+                mx[c >> 1] = fmaxf(mx[c >> 1], v);
+            }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 1));
+            mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 2));
+        }
+        if ((lane & 3) == 0) {
+            pmax[warp * LM_ROWS + r_lo] = mx[0];
+            pmax[warp * LM_ROWS + r_hi] = mx[1];
+        }
+        __syncthreads();
+        float m_new[2], corr[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int rr = k ? r_hi : r_lo;
+            const float tm = fmaxf(fmaxf(pmax[rr], pmax[LM_ROWS + rr]), fmaxf(pmax[2 * LM_ROWS + rr], pmax[3 * LM_ROWS + rr]));
+            m_new[k] = fmaxf(m_run[k], tm);
+            corr[k] = (m_run[k] == -INFINITY) ? 0.0f : expf(m_run[k] - m_new[k]);
+        }
+        float sm[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float p[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                p[c] = (sc[i][c] == -INFINITY) ? 0.0f : expf(sc[i][c] - m_new[c >> 1]);
+                sm[c >> 1] += p[c];
+            }
+            const int col = warp * 16 + i * 8 + 2 * (lane & 3);
+            *reinterpret_cast<__nv_bfloat162*>(p_s + r_lo * LDP + col) = __floats2bfloat162_rn(p[0], p[1]);
+            *reinterpret_cast<__nv_bfloat162*>(p_s + r_hi * LDP + col) = __floats2bfloat162_rn(p[2], p[3]);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            sm[k] += __shfl_xor_sync(0xffffffffu, sm[k], 1);
+            sm[k] += __shfl_xor_sync(0xffffffffu, sm[k], 2);
+        }
+        if ((lane & 3) == 0) {
+            psum[warp * LM_ROWS + r_lo] = sm[0];
+            psum[warp * LM_ROWS + r_hi] = sm[1];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int rr = k ? r_hi : r_lo;
+            l_run[k] = l_run[k] * corr[k] + ((psum[rr] + psum[LM_ROWS + rr]) + (psum[2 * LM_ROWS + rr] + psum[3 * LM_ROWS + rr]));
+            m_run[k] = m_new[k];
+        }
+        // ---- this warp's quarter of the sums over all 64 keys ------------------------------------------------
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < LM_KEYS / 16; ++kk) {
+            uint32_t a0, a1, a2, a3;
+            lm_ldmatrix_x4(a0, a1, a2, a3, p_s + (lane & 15) * LDP + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int i = 0; i < NT; i += 2) {
+                uint32_t b0, b1, b2, b3;
+                lm_ldmatrix_x4_trans(b0, b1, b2, b3, ct + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDC + warp * (R / 4) + i * 8 + (lane >> 4) * 8);
+                lm_mma(o[i], a0, a1, a2, a3, b0, b1);
+                if (i + 1 < NT) lm_mma(o[i + 1], a0, a1, a2, a3, b2, b3);   // an odd last tile: the other half read padding
+            }
+        }
+        __syncthreads();      // the buffer, P and the maxima are free for the next tile
+        if (t + 1 < t1) load_tile(t + 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // ---- out ------------------------------------------------------------------------------------------------
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int h = head0 + (k ? r_hi : r_lo);
+        if (h >= n_heads) continue;
+        if (n_slices == 1) {
+            const float inv = l_run[k] > 0.0f ? 1.0f / l_run[k] : 0.0f;
+            __nv_bfloat16* dst = out + (long)row * o_row + (long)h * o_head + warp * (R / 4) + 2 * (lane & 3);
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+                *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = __floats2bfloat162_rn(o[i][2 * k] * inv, o[i][2 * k + 1] * inv);
+        } else {
+            const long item = ((long)row * n_heads + h) * n_slices + slice;
+            float* dst = ws_acc + item * R + warp * (R / 4) + 2 * (lane & 3);
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                dst[i * 8] = o[i][2 * k];
+                dst[i * 8 + 1] = o[i][2 * k + 1];
+            }
+            if (warp == 0 && (lane & 3) == 0) {
+                ws_ml[item * 2] = m_run[k];
+                ws_ml[item * 2 + 1] = l_run[k];
+            }
+        }
     }
 }
+
+static IbDeviceSet latent_mma_smem_set[17];
+
+template <int NT>
+static int launch_latent_mma(const void* q, long q_row, long q_head, const void* plane, const int* block_table,
+                             int max_pages, int page_size, int n_pages, const int* row_request, const int* positions,
+                             int n_rows, int n_heads, float scale, int window, int n_slices, void* out, long o_row,
+                             long o_head, float* ws_acc, float* ws_ml, cudaStream_t stream) {
+    constexpr int R = 32 * NT, LDC = R + LM_PAD, LDP = LM_KEYS + LM_PAD;
+    const size_t smem = (size_t)(LM_ROWS * LDC + LM_KEYS * LDC + LM_ROWS * LDP) * 2 + 8 * LM_ROWS * sizeof(float);
+    if (smem > 48 * 1024) {
+        const int e = ib_allow_dynamic_smem(latent_mma_smem_set[NT], latent_attention_mma_kernel<NT>, smem);
+        if (e != IB_OK) return e;
+    }
+    const dim3 grid(n_rows, (n_heads + LM_ROWS - 1) / LM_ROWS, n_slices);
+    ib_launch(latent_attention_mma_kernel<NT>, grid, 128, smem, stream, (const __nv_bfloat16*)q, q_row, q_head,
+              (const __nv_bfloat16*)plane, block_table, max_pages, page_size, n_pages, row_request, positions, n_heads,
+              scale, window, n_slices, (__nv_bfloat16*)out, o_row, o_head, ws_acc, ws_ml);
+    return ib_launch_status();
+}
+#endif  // IB_ACT_BF16
 
 static IbDeviceSet latent_smem_set[2][5];
 
@@ -192,11 +455,35 @@ IB_EXPORT int ib_latent_attention(const void* q, int q_is_f32, long q_row, long 
                                   float scale, int window, int n_slices, void* out, long o_row, long o_head,
                                   float* ws_acc, float* ws_ml, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
-    if (n_heads <= 0 || R <= 0 || page_size <= 0 || max_pages <= 0 || n_slices <= 0 || n_slices > 65535 ||
+    if (n_heads <= 0 || R <= 0 || page_size <= 0 || max_pages <= 0 || n_slices <= 0 || n_slices > 64 ||
         (n_slices > 1 && (ws_acc == nullptr || ws_ml == nullptr)))
         return IB_ERR_ARGUMENT;
     if (R > 512) return IB_ERR_UNSUPPORTED;
     int e = IB_OK;
+#if IB_ACT_BF16
+    // bfloat16 queries and latents of a multiple of 32 numbers: the tensor cores
+    if (!q_is_f32 && R % 32 == 0 && page_size > 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)plane % 16) == 0) {
+        switch (R / 32) {
+#define IB_LATM(NT)                                                                                                  \
+        case NT: e = launch_latent_mma<NT>(q, q_row, q_head, plane, block_table, max_pages, page_size, n_pages,      \
+                                           row_request, positions, n_rows, n_heads, scale, window, n_slices, out,   \
+                                           o_row, o_head, ws_acc, ws_ml, stream); break;
+            IB_LATM(1) IB_LATM(2) IB_LATM(3) IB_LATM(4) IB_LATM(5) IB_LATM(6) IB_LATM(7) IB_LATM(8) IB_LATM(9)
+            IB_LATM(10) IB_LATM(11) IB_LATM(12) IB_LATM(13) IB_LATM(14) IB_LATM(15) IB_LATM(16)
+#undef IB_LATM
+            default: e = IB_ERR_UNSUPPORTED;
+        }
+        if (e != IB_ERR_UNSUPPORTED) {
+            if (e != IB_OK || n_slices == 1) return e;
+            const int jw = 4;
+            const long n_items = (long)n_rows * n_heads;
+            ib_launch(latent_attention_join_kernel, (unsigned)((n_items + jw - 1) / jw), 32 * jw, 0, stream, ws_acc, ws_ml,
+                      n_rows, n_heads, R, n_slices, (act_t*)out, o_row, o_head);
+            return ib_launch_status();
+        }
+        e = IB_OK;
+    }
+#endif
 #define IB_LAT(QT, QI, RPL, SI)                                                                                   \
     e = launch_latent<QT, RPL>(latent_smem_set[QI][SI], q, q_row, q_head, plane, block_table, max_pages, page_size, \
                                n_pages, row_request, positions, n_rows, n_heads, R, scale, window, n_slices, out,  \

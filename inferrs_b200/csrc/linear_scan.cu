@@ -31,7 +31,7 @@
 
 __device__ __forceinline__ float ls_logsigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
-template <int MODE>
+template <int MODE, int CH>   // CH tokens per chunk: 16, or 1 for steps of single tokens (few registers, many blocks per SM)
 __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col, int v_col,
                                    const float* __restrict__ gates, long ld_gates, const float* __restrict__ gate_bias,
                                    float gate_param, float q_scale, float* __restrict__ state, long slot_stride,
@@ -44,14 +44,14 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
     const int h = blockIdx.y, r = blockIdx.z, e0 = blockIdx.x * LS_COLS, d0 = warp * 32;
     const int row0 = q_start[r], row1 = q_start[r + 1];
     if (row1 <= row0) return;                           // the whole block leaves
-    float* q_s = smem;                                  // [LS_CHUNK][Dp]
-    float* k_s = q_s + LS_CHUNK * Dp;                   // [LS_CHUNK][Dp]   (mode 1: already times exp(i - m))
-    float* a_s = k_s + LS_CHUNK * Dp;                   // [LS_CHUNK][Dp]   mode 0: the decays
-    float* v_s = a_s + (MODE == 0 ? LS_CHUNK * Dp : 0); // [LS_CHUNK][32]
-    float* part = v_s + LS_CHUNK * LS_COLS;             // [LS_CHUNK][n_warps][32]
-    float* npart = part + LS_CHUNK * n_warps * LS_COLS; // [LS_CHUNK][n_warps]     mode 1
-    float* g_s = npart + LS_CHUNK * n_warps;            // [4][LS_CHUNK]           mode 1: i, f -> keep, take, exp(-m), m
-    float* m_s = g_s + 4 * LS_CHUNK;                    // [1]                     mode 1: the running maximum
+    float* q_s = smem;                                  // [CH][Dp]
+    float* k_s = q_s + CH * Dp;                   // [CH][Dp]   (mode 1: already times exp(i - m))
+    float* a_s = k_s + CH * Dp;                   // [CH][Dp]   mode 0: the decays
+    float* v_s = a_s + (MODE == 0 ? CH * Dp : 0); // [CH][32]
+    float* part = v_s + CH * LS_COLS;             // [CH][n_warps][32]
+    float* npart = part + CH * n_warps * LS_COLS; // [CH][n_warps]     mode 1
+    float* g_s = npart + CH * n_warps;            // [4][CH]           mode 1: i, f -> keep, take, exp(-m), m
+    float* m_s = g_s + 4 * CH;                    // [1]                     mode 1: the running maximum
 
     float* st = state + (long)slots[r] * slot_stride;
     float* st_S = st + (long)h * D * E;
@@ -82,20 +82,20 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
     // request's rows and the head's channels; what does not count is dropped when the registers are used): loads
     // under a condition are waited for one by one, loads without one are all under way together.  The numbers stay
     // as they were stored (act_t) until they are used, so nothing waits for them before the chunk is walked.
-    act_t rq[LS_CHUNK], rk[LS_CHUNK], rv[LS_CHUNK];
-    float rg[LS_CHUNK], r_gi = 0.0f, r_gf = 0.0f;
+    act_t rq[CH], rk[CH], rv[CH];
+    float rg[CH], r_gi = 0.0f, r_gf = 0.0f;
     const float my_bias = (MODE == 0 && d_ok) ? gate_bias[h * D + d_mine] : 0.0f;
     const int d_in = d_ok ? d_mine : D - 1;
     const int last_row = row1 - 1;
     auto fetch = [&](int c0) {
 #pragma unroll
-        for (int t = 0; t < LS_CHUNK; ++t) {
+        for (int t = 0; t < CH; ++t) {
             const act_t* p = proj + (long)min(c0 + t, last_row) * ld;
             rq[t] = p[q_col + h * D + d_in];
             rk[t] = p[k_col + h * D + d_in];
             if (MODE == 0) rg[t] = gates[(long)min(c0 + t, last_row) * ld_gates + h * D + d_in];
             const int idx = threadIdx.x + t * blockDim.x;          // the values: [tokens][32 columns]
-            const int vt = min(idx >> 5, LS_CHUNK - 1), ve = min(e0 + (idx & 31), E - 1);
+            const int vt = min(idx >> 5, CH - 1), ve = min(e0 + (idx & 31), E - 1);
             rv[t] = proj[(long)min(c0 + vt, last_row) * ld + v_col + h * E + ve];
         }
         if (MODE == 1 && warp == 0) {
@@ -106,11 +106,11 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
     };
     fetch(row0);
 
-    for (int c0 = row0; c0 < row1; c0 += LS_CHUNK) {
-        const int nc = min(LS_CHUNK, row1 - c0);
+    for (int c0 = row0; c0 < row1; c0 += CH) {
+        const int nc = min(CH, row1 - c0);
         // ---- the chunk's inputs from the registers to shared memory, gates turned into decays ---------------
 #pragma unroll
-        for (int t = 0; t < LS_CHUNK; ++t) {
+        for (int t = 0; t < CH; ++t) {
             if (t < nc) {
                 q_s[t * Dp + d_mine] = d_ok ? ib_to_float(rq[t]) * q_scale : 0.0f;
                 k_s[t * Dp + d_mine] = d_ok ? ib_to_float(rk[t]) : 0.0f;
@@ -138,15 +138,15 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
             __syncwarp();
             if (lane < nc) {
                 g_s[lane] = expf(lf + m_before - m_mine);              // keep
-                g_s[LS_CHUNK + lane] = expf(li - m_mine);              // take
-                g_s[2 * LS_CHUNK + lane] = expf(-m_mine);
+                g_s[CH + lane] = expf(li - m_mine);              // take
+                g_s[2 * CH + lane] = expf(-m_mine);
             }
             if (lane == 0) *m_s = m_prev;
         }
         __syncthreads();
-        if (c0 + LS_CHUNK < row1) fetch(c0 + LS_CHUNK);
+        if (c0 + CH < row1) fetch(c0 + CH);
         if (MODE == 1) {                                 // k times exp(i - m), once for all columns
-            for (int idx = threadIdx.x; idx < nc * Dp; idx += blockDim.x) k_s[idx] *= g_s[LS_CHUNK + idx / Dp];
+            for (int idx = threadIdx.x; idx < nc * Dp; idx += blockDim.x) k_s[idx] *= g_s[CH + idx / Dp];
             __syncthreads();
         }
         // ---- the tokens, one after the other ----------------------------------------------------------------
@@ -183,7 +183,7 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
             if (MODE == 1) {
                 float nq = 0.0f;
                 for (int w = 0; w < n_warps; ++w) nq += npart[t * n_warps + w];
-                o /= fmaxf(fabsf(nq), g_s[2 * LS_CHUNK + t]) + 1e-6f;
+                o /= fmaxf(fabsf(nq), g_s[2 * CH + t]) + 1e-6f;
             }
             if (e0 + e < E) out[((long)(c0 + t) * H + h) * E + e0 + e] = o;
         }
@@ -198,16 +198,17 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
     }
 }
 
-static IbDeviceSet scan_smem_set[2];
+static IbDeviceSet scan_smem_set[4];
 
 // proj [rows, ld] act_t holds q and k as [H, D] and v as [H, E] from columns q_col, k_col, v_col on.
 // gates [rows, ld_gates] float: mode 0 the decay's pre-activations [H, D] (gate_bias [H * D], gate_param = tau);
 // mode 1 the input gate's and then the forget gate's pre-activations [2, H] (gate_bias [2 * H], gate_param = cap).
-// out [rows, H, E] float.  state: see the head of the file; slot_stride floats per slot.
+// out [rows, H, E] float.  state: see the head of the file; slot_stride floats per slot.  max_rows: the most rows
+// that a request brings (1 chooses the form for steps of single tokens; any larger number the chunked form).
 IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int k_col, int v_col, const float* gates,
                              long ld_gates, const float* gate_bias, float gate_param, float q_scale, float* state,
                              long slot_stride, const int* q_start, const int* slots, int n_requests, float* out, int H,
-                             int D, int E, cudaStream_t stream) {
+                             int D, int E, int max_rows, cudaStream_t stream) {
     if (n_requests <= 0) return IB_OK;
     if (H <= 0 || D <= 0 || E <= 0 || proj == nullptr || gates == nullptr || gate_bias == nullptr || state == nullptr ||
         (mode != 0 && mode != 1) || !(gate_param > 0.0f))
@@ -218,21 +219,25 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
     const int n_warps = (D + 31) / 32;
     const dim3 grid((E + LS_COLS - 1) / LS_COLS, H, n_requests);
     const float param = mode == 0 ? 1.0f / gate_param : gate_param;
-    auto smem_for = [](int warps) {
-        return (size_t)(3 * LS_CHUNK * warps * 32 + LS_CHUNK * LS_COLS + LS_CHUNK * warps * LS_COLS + LS_CHUNK * warps +
-                        4 * LS_CHUNK + 4) * sizeof(float);
+    const int ch = max_rows == 1 ? 1 : LS_CHUNK;
+    auto smem_for = [ch](int warps) {
+        return (size_t)(3 * ch * warps * 32 + ch * LS_COLS + ch * warps * LS_COLS + ch * warps + 4 * ch + 4) * sizeof(float);
     };
     const size_t smem = smem_for(n_warps);
-    if (smem > 48 * 1024) {   // the permission is given once per device, for the most that the kernel can ask for
-        const int e = mode == 0 ? ib_allow_dynamic_smem(scan_smem_set[0], linear_scan_kernel<0>, smem_for(8))
-                                : ib_allow_dynamic_smem(scan_smem_set[1], linear_scan_kernel<1>, smem_for(8));
-        if (e != IB_OK) return e;
-    }
-    if (mode == 0)
-        ib_launch(linear_scan_kernel<0>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld, q_col, k_col, v_col,
-                  gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start, slots, out, H, D, E);
-    else
-        ib_launch(linear_scan_kernel<1>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld, q_col, k_col, v_col,
-                  gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start, slots, out, H, D, E);
+#define IB_SCAN(MODE, CH, SET)                                                                                       \
+    do {                                                                                                             \
+        if (smem > 48 * 1024) { /* the permission is given once per device, for the most that the kernel can ask */  \
+            const int e = ib_allow_dynamic_smem(scan_smem_set[SET], linear_scan_kernel<MODE, CH>, smem_for(8));      \
+            if (e != IB_OK) return e;                                                                                \
+        }                                                                                                            \
+        ib_launch(linear_scan_kernel<MODE, CH>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld, q_col,     \
+                  k_col, v_col, gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start, slots, out, \
+                  H, D, E);                                                                                          \
+    } while (0)
+    if (mode == 0 && ch == 1) IB_SCAN(0, 1, 0);
+    else if (mode == 0) IB_SCAN(0, LS_CHUNK, 1);
+    else if (ch == 1) IB_SCAN(1, 1, 2);
+    else IB_SCAN(1, LS_CHUNK, 3);
+#undef IB_SCAN
     return ib_launch_status();
 }

@@ -73,7 +73,7 @@ _SIGNATURES = {
     "ib_latent_norm_store": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                              c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p],
     "ib_linear_scan": [c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_float, c_float,
-                       c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ib_latent_attention": [c_void_p, c_int, c_long, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_long, c_long, c_void_p, c_void_p,
                             c_void_p],
@@ -308,7 +308,7 @@ SCAN_CHANNEL_DECAY, SCAN_SCALAR_GATES = 0, 1
 
 def linear_scan(mode: int, proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gates: torch.Tensor,
                 gate_bias: torch.Tensor, gate_param: float, q_scale: float, state: torch.Tensor, q_start: torch.Tensor,
-                slots: torch.Tensor, n_requests: int, out: torch.Tensor, key_dim: int):
+                slots: torch.Tensor, n_requests: int, out: torch.Tensor, key_dim: int, max_rows: int = 0):
     """A matrix state per head carried over each request's rows, one token after the other, in float32.
 
     SCAN_CHANNEL_DECAY:  S = diag(sigmoid(z + b)^(1/gate_param)) S + k v^T,  o = S^T (q * q_scale)
@@ -318,7 +318,8 @@ def linear_scan(mode: int, proj: torch.Tensor, q_col: int, k_col: int, v_col: in
 
     ``proj`` [rows, ld] holds q and k as [H, D] and v as [H, E] from the given columns on; ``gates`` float32 holds z
     [rows, H*D], or p and then r [rows, 2H]; ``out`` is float32 [rows, H, E]; ``state`` float32 [slots, ...] with at
-    least H*E*D (+ H*D + H) numbers per slot; request r's rows are q_start[r] .. q_start[r+1]-1, its slot slots[r]."""
+    least H*D*E (+ H*D + H) numbers per slot; request r's rows are q_start[r] .. q_start[r+1]-1, its slot slots[r].
+    ``max_rows``: the most rows that a request brings, if the caller knows (1: the form for steps of single tokens)."""
     act = proj.dtype
     _need(proj, "proj", _W, 2)
     _need(gates, "gates", (torch.float32,), 2)
@@ -340,20 +341,22 @@ def linear_scan(mode: int, proj: torch.Tensor, q_col: int, k_col: int, v_col: in
     _check(_core(act).ib_linear_scan(
         int(mode), _p(proj), proj.shape[1], q_col, k_col, v_col, _p(gates), gates.shape[1], _p(gate_bias),
         float(gate_param), float(q_scale), _p(state), slot_stride, _p(q_start), _p(slots), int(n_requests), _p(out),
-        heads, d_dim, e_dim, _stream()), "linear_scan")
+        heads, d_dim, e_dim, int(max_rows), _stream()), "linear_scan")
 
 
-LATENT_SLICE_KEYS = 256     # keys per slice when a row's keys are cut over several blocks
+LATENT_SLICE_KEYS = 128     # fewest keys per slice when a row's keys are cut over several blocks
+LATENT_RESIDENT_BLOCKS = 296   # two blocks of the tensor-core form per SM
 
 
 def latent_slices(n_rows: int, n_heads: int, max_kv_len: int) -> int:
-    """Into how many slices a row's keys are cut: one while the rows alone fill the machine, else so that about four
-    blocks per SM run, each slice with at least ``LATENT_SLICE_KEYS`` keys."""
+    """Into how many slices a row's keys are cut: one while the rows alone fill the machine, else as many as give
+    every SM its two blocks, each slice with at least ``LATENT_SLICE_KEYS`` keys (measured at 8 and 64 rows of 2,048
+    keys: 16 and 4 slices are the fastest)."""
     blocks = n_rows * ((n_heads + 15) // 16)
-    if blocks >= 296:
+    if blocks >= LATENT_RESIDENT_BLOCKS:
         return 1
     by_length = max(1, (max_kv_len + LATENT_SLICE_KEYS - 1) // LATENT_SLICE_KEYS)
-    return max(1, min(by_length, (592 + blocks - 1) // blocks, 64))
+    return max(1, min(by_length, (LATENT_RESIDENT_BLOCKS + blocks - 1) // blocks, 64))
 
 
 def latent_attention(q: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor, row_request: torch.Tensor,

@@ -160,7 +160,7 @@ def scan(args) -> dict:
     slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
     out = torch.empty(n, h, e, dtype=torch.float32, device=dev)
     fn = lambda: kernels.linear_scan(mode, proj, 0, h * d, 2 * h * d, gates, bias, 8.0, d ** -0.5, state, q_start,  # noqa: E731
-                                     slots, len(lens), out, d)
+                                     slots, len(lens), out, d, max(lens))
     us = _time(fn, args.iters)
     el = 4 if dtype == torch.float32 else 2
     byts = n * (2 * h * d + h * e) * el + n * gw * 4 + n * h * e * 4 + 2 * len(lens) * n_state * 4
@@ -196,7 +196,8 @@ def latent(args) -> dict:
     plane = torch.randn(n_pages, ps, r, device=dev).to(dtype)
     out = torch.empty(h, n, r, dtype=dtype, device=dev)
     slices = args.slices or kernels.latent_slices(n, h, max(lens))
-    fn = lambda: kernels.latent_attention(q, plane, table.to(dev), row_request, positions, r ** -0.5, None, out, slices)  # noqa: E731
+    table = table.to(dev)
+    fn = lambda: kernels.latent_attention(q, plane, table, row_request, positions, r ** -0.5, None, out, slices)  # noqa: E731
     us = _time(fn, args.iters)
     el = 4 if dtype == torch.float32 else 2
     pairs = sum(t * (c - t) + t * (t + 1) // 2 for c, t in zip(lens, new))

@@ -46,7 +46,7 @@ class _ScanMixer:
         o = torch.empty((n, s.n_heads, s.value_dim), dtype=torch.float32, device=h.device)
         kernels.linear_scan(mode, proj, self.cols[0], self.cols[1], self.cols[2], gates, gate_bias, gate_param,
                             float(s.key_dim) ** -0.5, ctx.storage.state(cache_id), ctx.q_start, ctx.slots,
-                            ctx.n_requests, o, s.key_dim)
+                            ctx.n_requests, o, s.key_dim, max_rows=ctx.max_q_len)
         gated = torch.empty((n, s.n_heads * s.value_dim), dtype=self.rt.dtype, device=h.device)
         kernels.head_norm_gate(o, proj[:, self.cols[3]:], self.out_norm, True, gate_act, s.eps, gated)
         return self.o(gated)

@@ -399,7 +399,10 @@ def paged_latents(c_per_request, page_size, n_pages, dtype, seed):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,R,window,slices", [(3, 36, None, 1), (18, 70, None, 1), (2, 130, 40, 1), (5, 300, None, 4),
-                                                (1, 512, 100, 3), (17, 24, None, 7)])
+                                                (1, 512, 100, 3), (17, 24, None, 7),
+                                                # ranks that the tensor-core form of the bfloat16 build takes
+                                                (6, 96, None, 1), (16, 128, None, 1), (3, 64, 40, 2), (40, 256, None, 3),
+                                                (33, 32, 70, 5), (16, 512, None, 2)])
 def test_latent_attention_kernel(H, R, window, slices, dtype):
     """A portion of one request (its later tokens are in the cache already and must stay unseen), a single token of
     another with many keys, and a first token; shuffled pages."""
@@ -426,13 +429,14 @@ def test_latent_attention_kernel(H, R, window, slices, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("R", [48, 64])
 @pytest.mark.parametrize("slices", [1, 5])
-def test_latent_attention_sees_exactly_its_keys(slices, dtype):
+def test_latent_attention_sees_exactly_its_keys(slices, R, dtype):
     """One latent of the cache is made to stand out (a large multiple of the query's direction), so that whoever
     sees it returns it: a key far back among hundreds, keys at page borders, the row's own key, the key just after
     it (a later token of the same portion), and with a window the keys just inside and just outside it."""
     from inferrs_b200 import kernels
-    R, H, page, n_keys, window = 48, 2, 16, 400, 64
+    H, page, n_keys, window = 2, 16, 400, 64
     g = torch.Generator().manual_seed(9)
     direction = torch.nn.functional.normalize(torch.randn(R, generator=g), dim=0)
     base = (0.1 * torch.randn(n_keys, R, generator=g))
