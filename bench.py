@@ -13,6 +13,13 @@ line's default sampling instead of greedy choice (``e2e_b8_sampled``), the batch
 of the published checkpoints (40,960: block tables and descriptions ten times as wide), and the two other
 workloads that the baseline names (Qwen3-0.6B shape, 256 requests at once; Qwen3-32B shape, 8 requests of
 8,192 tokens in portions of 2,048), each through the engine's own scheduler.
+
+    python bench.py --design vebonex [--design-layers N]
+
+is another workload (the default one stays as it is): prefill and decode throughput of the Vebonex design at two
+sizes that resemble a real model's layers, random weights, beside the Qwen3 shape of equal width, heads, head size,
+layers and feed-forward parameters, and the design's own kernels alone (the scans with a matrix state, the attention
+over cached latents) beside the Qwen3 attention kernels at equal sizes, each with its fraction of the measured peaks.
 """
 from __future__ import annotations
 
@@ -164,6 +171,131 @@ def workload(shape: dict, n_requests: int, prompt_lens, max_tokens: int, tokens_
     return out
 
 
+# ---- the Vebonex design beside the closest existing model -----------------------------------------------------
+def vebonex_config(width: int, heads: int, ff: int, q_rank: int, kv_rank: int, n_layers: int, vocab: int,
+                   positions: int) -> dict:
+    """Layers in the order scalar-gate scan, channel-decay scan, latent attention, latent attention on the same
+    latents, repeated; two streams, norms in four parts."""
+    def layer(i):
+        kind = i % 4
+        mlp = {"kind": "dense", "ff": ff}
+        if kind == 0:
+            return {"type": "mlstm", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}, "mlp": mlp}
+        if kind == 1:
+            return {"type": "gla", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "a_rank": 16}, "mlp": mlp}
+        m = {"heads": heads, "dim": 128, "vdim": 128, "q_rank": q_rank, "kv_rank": kv_rank, "scale": 128 ** -0.5}
+        if kind == 3:
+            m["kv_from"] = i - 1
+        return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+    return {"architecture": "Vebonex", "vocab": vocab, "width": width, "max_positions": positions, "streams": 2,
+            "norm": {"eps": 1e-5, "groups": 4}, "layers": [layer(i) for i in range(n_layers)]}
+
+
+def design_bench(args) -> int:
+    import argparse as ap_
+    import gc
+
+    import torch
+
+    from inferrs_b200 import kernels, microbench
+    from inferrs_b200.engine.batch import StepEntry
+    from inferrs_b200.engine.engine import Engine
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    vocab, positions, block, batch = 32000, 4096, 16, 8
+    gen = torch.Generator().manual_seed(1)
+
+    def measure(config):
+        eng = Engine(config=config, random_weights=0, dtype="bf16", block_size=block,
+                     num_blocks=(batch + 1) * positions // block, max_batch_size=batch, max_tokens_per_step=8192)
+        runner = eng.runner
+        times = []
+        for i in range(6):                                  # a 2,048-token prompt in one step
+            rid = ("p", i)
+            runner.admit(rid)
+            p = torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            runner.step([StepEntry(rid, p, [PROMPT_LEN - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            runner.release(rid)
+            if i >= 2:
+                times.append(a.elapsed_time(b))
+        pms = statistics.median(times)
+        rids = [("d", i) for i in range(batch)]            # decode: 8 requests, 2,048 tokens cached each
+        for i in range(0, batch, 4):
+            for r in rids[i:i + 4]:
+                runner.admit(r)
+            runner.step([StepEntry(r, torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist(), []) for r in rids[i:i + 4]])
+        toks = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+        out = torch.empty((batch,), dtype=torch.int32, device="cuda")
+
+        def one():
+            logits = runner.step([StepEntry(r, [t], [0]) for r, t in zip(rids, toks)], own_output=False)
+            kernels.argmax(logits, out, torch.bfloat16)
+        for _ in range(max(args.warmup, 3)):
+            one()
+        torch.cuda.synchronize()
+        n0 = kernels.launch_count()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.design_steps):
+            one()
+        b.record()
+        torch.cuda.synchronize()
+        dms = a.elapsed_time(b) / args.design_steps
+        launches = (kernels.launch_count() - n0) / args.design_steps
+        del eng, runner
+        gc.collect()
+        torch.cuda.empty_cache()
+        return {"prefill_ms": round(pms, 3), "prefill_tok_s": round(PROMPT_LEN * 1e3 / pms, 1),
+                "decode_ms_per_step": round(dms, 4), "decode_tok_s": round(batch * 1e3 / dms, 1),
+                "launches_per_decode_step": round(launches, 1)}
+
+    sizes = []
+    for name, width, heads, ff, q_rank, kv_rank in (("width 2048", 2048, 16, 8192, 768, 512),
+                                                    ("width 4096", 4096, 32, 16384, 1536, 512)):
+        n_layers = args.design_layers
+        ours = measure(vebonex_config(width, heads, ff, q_rank, kv_rank, n_layers, vocab, positions))
+        inner = (2 * ff // 3 + 255) // 256 * 256            # three matrices of the gated form against two: equal parameters
+        closest = measure({"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": n_layers,
+                           "hidden_size": width, "num_attention_heads": heads, "num_key_value_heads": heads // 4,
+                           "head_dim": 128, "intermediate_size": inner, "vocab_size": vocab, "rope_theta": 1e6,
+                           "rms_norm_eps": 1e-6, "max_position_embeddings": positions, "tie_word_embeddings": False,
+                           "hidden_act": "silu"})
+        sizes.append({"size": name, "layers": n_layers, "heads": heads, "ff": ff, "latent": kv_rank,
+                      "vebonex": ours, "qwen3_equal_size": closest})
+
+    # the design's own kernels alone, and the closest model's attention kernels at equal sizes
+    def ns(**kw):
+        return ap_.Namespace(iters=20, page_size=16, dtype="bf16", **kw)
+
+    def fractions(r):
+        r["frac_hbm"] = round(r["GBps"] / pk["hbm_gbs"], 4)
+        r["frac_bf16"] = round(r["TFLOPs"] / pk["bf16_tflops"], 4)
+        return r
+    rows = []
+    for heads in (16, 32):
+        for mode in ("gates", "decay"):
+            rows.append(microbench.scan(ns(mode=mode, form="prefill", batch=1, tokens=2048, heads=heads, key_dim=128, value_dim=128)))
+            for b in (8, 64):
+                rows.append(microbench.scan(ns(mode=mode, form="decode", batch=b, tokens=1, heads=heads, key_dim=128, value_dim=128)))
+        rows.append(microbench.latent(ns(form="prefill", batch=1, context=2048, tokens=2048, context_before=0, heads=heads, rank=512, slices=0)))
+        rows.append(microbench.attention(ns(form="prefill", impl="tcgen05-pair", batch=1, context=2048, tokens=2048, context_before=0,
+                                            splits=0, min_tiles=0, max_context=0, heads=heads, kv_heads=heads // 4, head_dim=128)))
+        for b in (8, 64):
+            rows.append(microbench.latent(ns(form="decode", batch=b, context=2048, tokens=1, context_before=0, heads=heads, rank=512, slices=0)))
+            rows.append(microbench.attention(ns(form="decode", impl="tcgen05", batch=b, context=2048, tokens=1, context_before=0,
+                                                splits=0, min_tiles=0, max_context=0, heads=heads, kv_heads=heads // 4, head_dim=128)))
+    print(json.dumps({"design": "Vebonex", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights",
+                      "prompt_len": PROMPT_LEN, "decode_batch": batch, "decode_steps": args.design_steps,
+                      "peaks": pk, "sizes": sizes, "kernels": [fractions(r) for r in rows]}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -175,6 +307,9 @@ def main() -> int:
     ap.add_argument("--clock-interval-ms", type=int, default=200, help="how often nvidia-smi is asked for the clocks")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points and the prefill")
     ap.add_argument("--no-workloads", action="store_true", help="skip the Qwen3-0.6B and Qwen3-32B workloads")
+    ap.add_argument("--design", choices=["vebonex"], help="another workload: this design beside the closest model")
+    ap.add_argument("--design-layers", type=int, default=8, help="layers of both models of --design")
+    ap.add_argument("--design-steps", type=int, default=64, help="timed decode steps of --design")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -186,6 +321,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design:
+        return design_bench(args)
 
     import gc
 
