@@ -12,12 +12,12 @@
 // builds; q, k and v come from a projection in act_t.  A request's rows are walked in order, one token after the
 // other, so a result does not depend on how the prompt was cut into steps or on what else the step holds.
 //
-// Work split: a block owns 32 columns of S for one (request, head); lane l owns column l, warp w the rows 32 w ..
-// 32 w + 31, each lane's 32 numbers of S in registers.  Tokens go in chunks of 16: the block fetches the chunk's q, k,
+// Work split: a block owns 32 columns of S for one (request, head); lane l owns column l, warp w the rows 16 w ..
+// 16 w + 15, each lane's 16 numbers of S in registers.  Tokens go in chunks of 16: the block fetches the chunk's q, k,
 // v and gates together, a chunk ahead (one trip to memory per chunk, under the walk of the chunk before), turns the gates into
 // decays there with all threads (the exponentials, logarithms and hyperbolic tangents leave the sequential part;
 // of the running maximum only a chain of additions and comparisons stays sequential), then every warp walks the
-// chunk's tokens: per token 32 multiply-adds per lane for the update and 32 for the product with q, all operands but
+// chunk's tokens: per token 16 multiply-adds per lane for the update and 16 for the product with q, all operands but
 // S and v read from shared memory as the same word for the whole warp.  The warps' partial products are summed
 // through shared memory once per chunk.  In mode 1 the vector n is kept a row per lane by every warp for its rows,
 // and n . q is a warp sum per token that does not stand in the way of the update.
@@ -31,6 +31,9 @@
 
 __device__ __forceinline__ float ls_logsigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
+#define LS_RW 16      // rows of S per warp
+#define LS_TOK(CH) ((CH) > 1 ? (CH) / 2 : 1)   // tokens of a chunk that a thread fetches
+
 template <int MODE, int CH>   // CH tokens per chunk: 16, or 1 for steps of single tokens (few registers, many blocks per SM)
 __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col, int v_col,
                                    const float* __restrict__ gates, long ld_gates, const float* __restrict__ gate_bias,
@@ -40,18 +43,18 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
     extern __shared__ __align__(16) float smem[];
     ib_grid_dependency_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    const int Dp = n_warps * 32;                        // D rounded up: the rows beyond D hold zeros
-    const int h = blockIdx.y, r = blockIdx.z, e0 = blockIdx.x * LS_COLS, d0 = warp * 32;
+    const int Dp = n_warps * LS_RW;                     // D rounded up: the rows beyond D hold zeros
+    const int h = blockIdx.y, r = blockIdx.z, e0 = blockIdx.x * LS_COLS, d0 = warp * LS_RW;
     const int row0 = q_start[r], row1 = q_start[r + 1];
     if (row1 <= row0) return;                           // the whole block leaves
     float* q_s = smem;                                  // [CH][Dp]
-    float* k_s = q_s + CH * Dp;                   // [CH][Dp]   (mode 1: already times exp(i - m))
-    float* a_s = k_s + CH * Dp;                   // [CH][Dp]   mode 0: the decays
-    float* v_s = a_s + (MODE == 0 ? CH * Dp : 0); // [CH][32]
-    float* part = v_s + CH * LS_COLS;             // [CH][n_warps][32]
-    float* npart = part + CH * n_warps * LS_COLS; // [CH][n_warps]     mode 1
-    float* g_s = npart + CH * n_warps;            // [4][CH]           mode 1: i, f -> keep, take, exp(-m), m
-    float* m_s = g_s + 4 * CH;                    // [1]                     mode 1: the running maximum
+    float* k_s = q_s + CH * Dp;                         // [CH][Dp]
+    float* a_s = k_s + CH * Dp;                         // [CH][Dp]   mode 0: the decays
+    float* v_s = a_s + (MODE == 0 ? CH * Dp : 0);       // [CH][32]
+    float* part = v_s + CH * LS_COLS;                   // [CH][n_warps][32]
+    float* npart = part + CH * n_warps * LS_COLS;       // [CH][n_warps]     mode 1
+    float* g_s = npart + CH * n_warps;                  // [3][CH]           mode 1: keep, take, exp(-m)
+    float* m_s = g_s + 4 * CH;                          // [1]               mode 1: the running maximum
 
     float* st = state + (long)slots[r] * slot_stride;
     float* st_S = st + (long)h * D * E;
@@ -59,44 +62,49 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
     float* st_m = st + (long)H * D * E + (long)H * D + h;
     const bool col_ok = e0 + lane < E;
 
-    // the state's loads carry no condition either (see the chunk's loads below): the address is brought inside
-    float S[32];
+    // the state's loads carry no condition (see the chunk's loads below): the address is brought inside
+    float S[LS_RW];
     const int e_in = min(e0 + lane, E - 1);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) S[i] = st_S[(long)min(d0 + i, D - 1) * E + e_in];
+    for (int i = 0; i < LS_RW; ++i) S[i] = st_S[(long)min(d0 + i, D - 1) * E + e_in];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) S[i] = (col_ok && d0 + i < D) ? S[i] : 0.0f;
-    float n_row = 0.0f;                                 // mode 1: n of row d0 + lane
+    for (int i = 0; i < LS_RW; ++i) S[i] = (col_ok && d0 + i < D) ? S[i] : 0.0f;
+    const bool n_mine = lane < LS_RW && d0 + lane < D;  // mode 1: lanes 0..15 keep n of the rows d0 + lane
+    float n_row = 0.0f;
     if (MODE == 1) {
-        if (d0 + lane < D) n_row = st_n[d0 + lane];
+        if (n_mine) n_row = st_n[d0 + lane];
         if (threadIdx.x == 0) *m_s = *st_m;
     }
     __syncthreads();
 
-    // One chunk's inputs as every thread fetches them: thread d owns key channel d of all the chunk's tokens (the
-    // block has Dp threads), and a share of the chunk's values.  They are asked for a chunk ahead and wait in
-    // registers while the chunk before is walked, so a trip to memory is paid once and under cover.
-    const int d_mine = threadIdx.x;
-    const bool d_ok = d_mine < D;
+    // One chunk's inputs as every thread fetches them: the block has 2 Dp threads; thread (d, half) owns key channel
+    // d of the chunk's tokens of that parity, and a share of the chunk's values.  They are asked for a chunk ahead and
+    // wait in registers while the chunk before is walked, so a trip to memory is paid once and under cover.
     // Every load is issued whatever the chunk's length and the thread's channel (the address is brought inside the
     // request's rows and the head's channels; what does not count is dropped when the registers are used): loads
     // under a condition are waited for one by one, loads without one are all under way together.  The numbers stay
     // as they were stored (act_t) until they are used, so nothing waits for them before the chunk is walked.
-    act_t rq[CH], rk[CH], rv[CH];
-    float rg[CH], r_gi = 0.0f, r_gf = 0.0f;
+    constexpr int NT = LS_TOK(CH);
+    const int half = threadIdx.x >= Dp ? 1 : 0;
+    const int d_mine = threadIdx.x - half * Dp;
+    const bool d_ok = d_mine < D;
+    const bool fetches = CH > 1 || half == 0;
+    act_t rq[NT], rk[NT], rv[NT];
+    float rg[NT], r_gi = 0.0f, r_gf = 0.0f;
     const float my_bias = (MODE == 0 && d_ok) ? gate_bias[h * D + d_mine] : 0.0f;
     const int d_in = d_ok ? d_mine : D - 1;
     const int last_row = row1 - 1;
     auto fetch = [&](int c0) {
 #pragma unroll
-        for (int t = 0; t < CH; ++t) {
+        for (int i = 0; i < NT; ++i) {
+            const int t = CH > 1 ? 2 * i + half : 0;
             const act_t* p = proj + (long)min(c0 + t, last_row) * ld;
-            rq[t] = p[q_col + h * D + d_in];
-            rk[t] = p[k_col + h * D + d_in];
-            if (MODE == 0) rg[t] = gates[(long)min(c0 + t, last_row) * ld_gates + h * D + d_in];
-            const int idx = threadIdx.x + t * blockDim.x;          // the values: [tokens][32 columns]
+            rq[i] = p[q_col + h * D + d_in];
+            rk[i] = p[k_col + h * D + d_in];
+            if (MODE == 0) rg[i] = gates[(long)min(c0 + t, last_row) * ld_gates + h * D + d_in];
+            const int idx = threadIdx.x + i * blockDim.x;          // the values: [tokens][32 columns]
             const int vt = min(idx >> 5, CH - 1), ve = min(e0 + (idx & 31), E - 1);
-            rv[t] = proj[(long)min(c0 + vt, last_row) * ld + v_col + h * E + ve];
+            rv[i] = proj[(long)min(c0 + vt, last_row) * ld + v_col + h * E + ve];
         }
         if (MODE == 1 && warp == 0) {
             const float* gp = gates + (long)min(c0 + lane, last_row) * ld_gates;
@@ -110,15 +118,16 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
         const int nc = min(CH, row1 - c0);
         // ---- the chunk's inputs from the registers to shared memory, gates turned into decays ---------------
 #pragma unroll
-        for (int t = 0; t < CH; ++t) {
-            if (t < nc) {
-                q_s[t * Dp + d_mine] = d_ok ? ib_to_float(rq[t]) * q_scale : 0.0f;
-                k_s[t * Dp + d_mine] = d_ok ? ib_to_float(rk[t]) : 0.0f;
+        for (int i = 0; i < NT; ++i) {
+            const int t = CH > 1 ? 2 * i + half : 0;
+            if (t < nc && fetches) {
+                q_s[t * Dp + d_mine] = d_ok ? ib_to_float(rq[i]) * q_scale : 0.0f;
+                k_s[t * Dp + d_mine] = d_ok ? ib_to_float(rk[i]) : 0.0f;
                 if (MODE == 0)
-                    a_s[t * Dp + d_mine] = d_ok ? expf(ls_logsigmoid(rg[t] + my_bias) * gate_param) : 1.0f;   // 1 / tau
+                    a_s[t * Dp + d_mine] = d_ok ? expf(ls_logsigmoid(rg[i] + my_bias) * gate_param) : 1.0f;   // 1 / tau
             }
-            const int idx = threadIdx.x + t * blockDim.x;
-            if (idx < nc * LS_COLS) v_s[idx] = (e0 + (idx & 31) < E) ? ib_to_float(rv[t]) : 0.0f;
+            const int idx = threadIdx.x + i * blockDim.x;
+            if (idx < nc * LS_COLS) v_s[idx] = (e0 + (idx & 31) < E) ? ib_to_float(rv[i]) : 0.0f;
         }
         if (MODE == 1 && warp == 0) {
             const float cap = gate_param;
@@ -138,27 +147,42 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
             __syncwarp();
             if (lane < nc) {
                 g_s[lane] = expf(lf + m_before - m_mine);              // keep
-                g_s[CH + lane] = expf(li - m_mine);              // take
+                g_s[CH + lane] = expf(li - m_mine);                    // take
                 g_s[2 * CH + lane] = expf(-m_mine);
             }
             if (lane == 0) *m_s = m_prev;
         }
         __syncthreads();
         if (c0 + CH < row1) fetch(c0 + CH);
-        if (MODE == 1) {                                 // k times exp(i - m), once for all columns
-            for (int idx = threadIdx.x; idx < nc * Dp; idx += blockDim.x) k_s[idx] *= g_s[CH + idx / Dp];
-            __syncthreads();
+        if (MODE == 1) {
+            // n of this warp's rows over the chunk, and its products with q: the recurrence is one multiply-add a token,
+            // the sixteen warp sums do not depend on one another and leave the walk below alone
+            float pq[CH];
+            const int dn = d0 + (lane & (LS_RW - 1));
+#pragma unroll
+            for (int t = 0; t < CH; ++t) {
+                pq[t] = 0.0f;
+                if (t < nc) {
+                    n_row = n_mine ? fmaf(g_s[t], n_row, g_s[CH + t] * k_s[t * Dp + dn]) : 0.0f;
+                    pq[t] = n_row * q_s[t * Dp + dn];
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < CH; ++t) pq[t] = ib_warp_sum(pq[t]);
+#pragma unroll
+            for (int t = 0; t < CH; ++t)
+                if (lane == t && t < nc) npart[t * n_warps + warp] = pq[t];
         }
         // ---- the tokens, one after the other ----------------------------------------------------------------
         for (int t = 0; t < nc; ++t) {
-            const float vt = v_s[t * LS_COLS + lane];
+            const float vt = MODE == 1 ? v_s[t * LS_COLS + lane] * g_s[CH + t] : v_s[t * LS_COLS + lane];   // v times exp(i - m)
             const float4* q4 = reinterpret_cast<const float4*>(q_s + t * Dp + d0);
             const float4* k4 = reinterpret_cast<const float4*>(k_s + t * Dp + d0);
             const float4* a4 = reinterpret_cast<const float4*>(a_s + t * Dp + d0);
             const float keep = MODE == 1 ? g_s[t] : 0.0f;
             float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < LS_RW / 4; ++i) {
                 const float4 q = q4[i], k = k4[i];
                 float4 a;
                 if (MODE == 0) a = a4[i]; else a = make_float4(keep, keep, keep, keep);
@@ -168,11 +192,6 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
                 S[4 * i + 3] = fmaf(a.w, S[4 * i + 3], k.w * vt); acc3 = fmaf(S[4 * i + 3], q.w, acc3);
             }
             part[(t * n_warps + warp) * LS_COLS + lane] = (acc0 + acc1) + (acc2 + acc3);
-            if (MODE == 1) {
-                n_row = fmaf(keep, n_row, k_s[t * Dp + d0 + lane]);
-                const float nq = ib_warp_sum(n_row * q_s[t * Dp + d0 + lane]);
-                if (lane == 0) npart[t * n_warps + warp] = nq;
-            }
         }
         __syncthreads();
         // ---- the warps' shares of every token's product, summed ---------------------------------------------
@@ -190,10 +209,10 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
+    for (int i = 0; i < LS_RW; ++i)
         if (col_ok && d0 + i < D) st_S[(long)(d0 + i) * E + e0 + lane] = S[i];
     if (MODE == 1 && blockIdx.x == 0) {
-        if (d0 + lane < D) st_n[d0 + lane] = n_row;
+        if (n_mine) st_n[d0 + lane] = n_row;
         if (threadIdx.x == 0) *st_m = *m_s;
     }
 }
@@ -216,18 +235,18 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
     if (D > 256 || H > 65535 || n_requests > 65535) return IB_ERR_UNSUPPORTED;
     const long need = (long)H * E * D + (mode == 1 ? (long)H * D + H : 0);
     if (slot_stride < need) return IB_ERR_ARGUMENT;
-    const int n_warps = (D + 31) / 32;
+    const int n_warps = D <= 16 ? 2 : (D + LS_RW - 1) / LS_RW;     // at least two: a thread per (channel, token parity)
     const dim3 grid((E + LS_COLS - 1) / LS_COLS, H, n_requests);
     const float param = mode == 0 ? 1.0f / gate_param : gate_param;
     const int ch = max_rows == 1 ? 1 : LS_CHUNK;
     auto smem_for = [ch](int warps) {
-        return (size_t)(3 * ch * warps * 32 + ch * LS_COLS + ch * warps * LS_COLS + ch * warps + 4 * ch + 4) * sizeof(float);
+        return (size_t)(3 * ch * warps * LS_RW + ch * LS_COLS + ch * warps * LS_COLS + ch * warps + 4 * ch + 4) * sizeof(float);
     };
     const size_t smem = smem_for(n_warps);
 #define IB_SCAN(MODE, CH, SET)                                                                                       \
     do {                                                                                                             \
         if (smem > 48 * 1024) { /* the permission is given once per device, for the most that the kernel can ask */  \
-            const int e = ib_allow_dynamic_smem(scan_smem_set[SET], linear_scan_kernel<MODE, CH>, smem_for(8));      \
+            const int e = ib_allow_dynamic_smem(scan_smem_set[SET], linear_scan_kernel<MODE, CH>, smem_for(16));      \
             if (e != IB_OK) return e;                                                                                \
         }                                                                                                            \
         ib_launch(linear_scan_kernel<MODE, CH>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld, q_col,     \
