@@ -34,8 +34,11 @@ __device__ __forceinline__ float ls_logsigmoid(float z) { return fminf(z, 0.0f) 
 #define LS_RW 16      // rows of S per warp
 #define LS_TOK(CH) ((CH) > 1 ? (CH) / 2 : 1)   // tokens of a chunk that a thread fetches
 
-template <int MODE, int CH>   // CH tokens per chunk: 16, or 1 for steps of single tokens (few registers, many blocks per SM)
-__global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col, int v_col,
+// CH tokens per chunk: 16, or 1 for steps of single tokens (few registers, many blocks per SM).  MAXT: the most
+// threads of a block, 256 (up to 128 key channels) or 512 (up to 256): the registers must allow that many.
+template <int MODE, int CH, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col, int v_col,
                                    const float* __restrict__ gates, long ld_gates, const float* __restrict__ gate_bias,
                                    float gate_param, float q_scale, float* __restrict__ state, long slot_stride,
                                    const int* __restrict__ q_start, const int* __restrict__ slots,
@@ -217,7 +220,7 @@ __global__ void linear_scan_kernel(const act_t* __restrict__ proj, long ld, int 
     }
 }
 
-static IbDeviceSet scan_smem_set[4];
+static IbDeviceSet scan_smem_set[8];
 
 // proj [rows, ld] act_t holds q and k as [H, D] and v as [H, E] from columns q_col, k_col, v_col on.
 // gates [rows, ld_gates] float: mode 0 the decay's pre-activations [H, D] (gate_bias [H * D], gate_param = tau);
@@ -243,20 +246,25 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
         return (size_t)(3 * ch * warps * LS_RW + ch * LS_COLS + ch * warps * LS_COLS + ch * warps + 4 * ch + 4) * sizeof(float);
     };
     const size_t smem = smem_for(n_warps);
-#define IB_SCAN(MODE, CH, SET)                                                                                       \
+#define IB_SCAN_T(MODE, CH, MAXT, SET)                                                                               \
     do {                                                                                                             \
         if (smem > 48 * 1024) { /* the permission is given once per device, for the most that the kernel can ask */  \
-            const int e = ib_allow_dynamic_smem(scan_smem_set[SET], linear_scan_kernel<MODE, CH>, smem_for(16));      \
+            const int e = ib_allow_dynamic_smem(scan_smem_set[SET], linear_scan_kernel<MODE, CH, MAXT>, smem_for(16)); \
             if (e != IB_OK) return e;                                                                                \
         }                                                                                                            \
-        ib_launch(linear_scan_kernel<MODE, CH>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld, q_col,     \
-                  k_col, v_col, gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start, slots, out, \
-                  H, D, E);                                                                                          \
+        ib_launch(linear_scan_kernel<MODE, CH, MAXT>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld,      \
+                  q_col, k_col, v_col, gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start,      \
+                  slots, out, H, D, E);                                                                              \
+    } while (0)
+#define IB_SCAN(MODE, CH, SET)                                                                                       \
+    do {                                                                                                             \
+        if (32 * n_warps <= 256) IB_SCAN_T(MODE, CH, 256, SET); else IB_SCAN_T(MODE, CH, 512, SET + 4);              \
     } while (0)
     if (mode == 0 && ch == 1) IB_SCAN(0, 1, 0);
     else if (mode == 0) IB_SCAN(0, LS_CHUNK, 1);
     else if (ch == 1) IB_SCAN(1, 1, 2);
     else IB_SCAN(1, LS_CHUNK, 3);
+#undef IB_SCAN_T
 #undef IB_SCAN
     return ib_launch_status();
 }

@@ -63,13 +63,15 @@ IB_EXPORT int ib_embedding_streams(const void* table, int table_is_f32, const in
 // rows != nullptr : row rows[r] -> row r of out; nothing is written back (the last norm of a model).
 // Everything in float32; only `out` is act_t.
 // ---------------------------------------------------------------------------
+struct alignas(sizeof(act_t) * 4) StreamVec4 { act_t v[4]; };
+
 template <typename WT>
 __global__ void stream_add_norm_kernel(float* __restrict__ residual, const act_t* __restrict__ delta,
                                        const float* __restrict__ mix, const float* __restrict__ gain,
                                        const float* __restrict__ read, const WT* __restrict__ weight,
                                        act_t* __restrict__ out, const int* __restrict__ rows, int streams, int width,
                                        int groups, float eps) {
-    extern __shared__ float u_row[];          // [width]
+    extern __shared__ __align__(16) float u_row[];          // [width]
     __shared__ float red[32];
     __shared__ float inv_g[IB_MAX_GROUPS];
     __shared__ float s_mix[IB_MAX_STREAMS * IB_MAX_STREAMS], s_gain[IB_MAX_STREAMS], s_read[IB_MAX_STREAMS];
@@ -87,31 +89,63 @@ __global__ void stream_add_norm_kernel(float* __restrict__ residual, const act_t
     float* res = residual + (size_t)src * S * width;
     const act_t* del = delta ? delta + (size_t)src * width : nullptr;
     const bool write_back = (rows == nullptr) && (del != nullptr);
-    for (int j = threadIdx.x; j < width; j += blockDim.x) {
-        float x[IB_MAX_STREAMS];
+    // Four columns a thread and step where the width allows it (16-byte loads of every stream); loads carry no
+    // condition (a stream beyond the last is read as the last and dropped), so all of a step's loads are under way together.
+    const bool vec = (width & 3) == 0 && (((uintptr_t)res | (uintptr_t)del | (uintptr_t)u_row) & 15) == 0;
+    const int step = vec ? 4 : 1;
+    for (int j = threadIdx.x * step; j < width; j += blockDim.x * step) {
+        float x[IB_MAX_STREAMS][4], d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int s = 0; s < IB_MAX_STREAMS; ++s) x[s] = s < S ? res[(size_t)s * width + j] : 0.0f;
-        float u = 0.0f;
+        for (int s = 0; s < IB_MAX_STREAMS; ++s) {
+            const float* src = res + (size_t)min(s, S - 1) * width + j;
+            if (vec) {
+                const float4 v = *reinterpret_cast<const float4*>(src);
+                x[s][0] = v.x; x[s][1] = v.y; x[s][2] = v.z; x[s][3] = v.w;
+            } else {
+                x[s][0] = *src; x[s][1] = x[s][2] = x[s][3] = 0.0f;
+            }
+        }
         if (del) {
-            const float d = ib_to_float(del[j]);
+            if (vec) {
+                const StreamVec4 v = *reinterpret_cast<const StreamVec4*>(del + j);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) d[c] = ib_to_float(v.v[c]);
+            } else {
+                d[0] = ib_to_float(del[j]);
+            }
+        }
+        float u[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (del) {
 #pragma unroll
             for (int t = 0; t < IB_MAX_STREAMS; ++t) {
                 if (t < S) {
-                    float v = 0.0f;
+                    float v[4];
 #pragma unroll
-                    for (int s = 0; s < IB_MAX_STREAMS; ++s)
-                        if (s < S) v = fmaf(s_mix[s * S + t], x[s], v);
-                    v = fmaf(s_gain[t], d, v);
-                    if (write_back) res[(size_t)t * width + j] = v;
-                    u = fmaf(s_read[t], v, u);
+                    for (int c = 0; c < 4; ++c) {
+                        v[c] = 0.0f;
+#pragma unroll
+                        for (int s2 = 0; s2 < IB_MAX_STREAMS; ++s2)
+                            if (s2 < S) v[c] = fmaf(s_mix[s2 * S + t], x[s2][c], v[c]);
+                        v[c] = fmaf(s_gain[t], d[c], v[c]);
+                        u[c] = fmaf(s_read[t], v[c], u[c]);
+                    }
+                    if (write_back) {
+                        float* dst = res + (size_t)t * width + j;
+                        if (vec) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                        else *dst = v[0];
+                    }
                 }
             }
         } else {
 #pragma unroll
             for (int t = 0; t < IB_MAX_STREAMS; ++t)
-                if (t < S) u = fmaf(s_read[t], x[t], u);
+                if (t < S) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) u[c] = fmaf(s_read[t], x[t][c], u[c]);
+                }
         }
-        u_row[j] = u;
+        if (vec) *reinterpret_cast<float4*>(u_row + j) = make_float4(u[0], u[1], u[2], u[3]);
+        else u_row[j] = u[0];
     }
     __syncthreads();
     const int part = width / groups;
@@ -230,6 +264,11 @@ IB_EXPORT int ib_head_norm_gate(const void* o, int o_is_f32, long o_row, long o_
 //     out = a * z / r1 + b * z^2 / r2 + c * z^3 / r3 + e,     r_p = sqrt(mean((z^p)^2) + eps)
 // coef = (a, b, c, e) in float32.  Powers element by element; sums in float32.
 // ---------------------------------------------------------------------------
+#define POLY_VEC (16 / (int)sizeof(act_t))      // elements per 16-byte load: 8 bfloat16 or 4 float
+#define POLY_KEEP 4                             // loads that a thread keeps in registers between the two passes
+struct alignas(16) PolyVec { act_t v[POLY_VEC]; };
+
+template <bool VEC>
 __global__ void poly_norm_kernel(const act_t* __restrict__ z, const float* __restrict__ coef, act_t* __restrict__ out,
                                  int width, float eps) {
     __shared__ float red[32];
@@ -237,7 +276,49 @@ __global__ void poly_norm_kernel(const act_t* __restrict__ z, const float* __res
     const float a = coef[0], b = coef[1], c = coef[2], e = coef[3];
     ib_grid_dependency_wait();
     const act_t* src = z + (size_t)blockIdx.x * width;
+    act_t* dst = out + (size_t)blockIdx.x * width;
     float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    if (VEC) {
+        // the host picks a block that holds the row in POLY_KEEP loads per thread: the row is read once
+        const int nv = width / POLY_VEC;
+        const PolyVec* src_v = reinterpret_cast<const PolyVec*>(src);
+        PolyVec keep[POLY_KEEP];
+#pragma unroll
+        for (int k = 0; k < POLY_KEEP; ++k) keep[k] = src_v[min((int)(threadIdx.x + k * blockDim.x), nv - 1)];
+#pragma unroll
+        for (int k = 0; k < POLY_KEEP; ++k) {
+            if ((int)(threadIdx.x + k * blockDim.x) < nv) {
+#pragma unroll
+                for (int i = 0; i < POLY_VEC; ++i) {
+                    const float v = ib_to_float(keep[k].v[i]);
+                    const float v2 = v * v, v3 = v2 * v;
+                    s1 += v2; s2 += v2 * v2; s3 += v3 * v3;
+                }
+            }
+        }
+        s1 = ib_block_sum(s1, red);
+        s2 = ib_block_sum(s2, red);
+        s3 = ib_block_sum(s3, red);
+        const float k1 = a / sqrtf(s1 / (float)width + eps);
+        const float k2 = b / sqrtf(s2 / (float)width + eps);
+        const float k3 = c / sqrtf(s3 / (float)width + eps);
+        PolyVec* dst_v = reinterpret_cast<PolyVec*>(dst);
+#pragma unroll
+        for (int k = 0; k < POLY_KEEP; ++k) {
+            const int j = threadIdx.x + k * blockDim.x;
+            if (j < nv) {
+                PolyVec o;
+#pragma unroll
+                for (int i = 0; i < POLY_VEC; ++i) {
+                    const float v = ib_to_float(keep[k].v[i]);
+                    const float v2 = v * v;
+                    o.v[i] = ib_from_float<act_t>(k1 * v + k2 * v2 + k3 * (v2 * v) + e);
+                }
+                dst_v[j] = o;
+            }
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
         const float v = ib_to_float(src[j]);
         const float v2 = v * v, v3 = v2 * v;
@@ -251,7 +332,6 @@ __global__ void poly_norm_kernel(const act_t* __restrict__ z, const float* __res
     const float k1 = a / sqrtf(s1 / (float)width + eps);
     const float k2 = b / sqrtf(s2 / (float)width + eps);
     const float k3 = c / sqrtf(s3 / (float)width + eps);
-    act_t* dst = out + (size_t)blockIdx.x * width;
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
         const float v = ib_to_float(src[j]);
         const float v2 = v * v;
@@ -263,8 +343,17 @@ IB_EXPORT int ib_poly_norm(const void* z, const float* coef, void* out, int n_ro
                            cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (width <= 0 || coef == nullptr) return IB_ERR_ARGUMENT;
-    const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
-    ib_launch(poly_norm_kernel, n_rows, threads, 0, stream, (const act_t*)z, coef, (act_t*)out, width, eps);
+    // 16-byte loads and the row in registers where the width is a multiple of a load and POLY_KEEP loads per thread
+    // of a block of up to 1,024 threads hold it
+    const int nv = width / POLY_VEC;
+    if (width % POLY_VEC == 0 && nv <= POLY_KEEP * 1024 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0) {
+        int threads = 128;
+        while (threads * POLY_KEEP < nv) threads <<= 1;
+        ib_launch(poly_norm_kernel<true>, n_rows, threads, 0, stream, (const act_t*)z, coef, (act_t*)out, width, eps);
+    } else {
+        const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+        ib_launch(poly_norm_kernel<false>, n_rows, threads, 0, stream, (const act_t*)z, coef, (act_t*)out, width, eps);
+    }
     return ib_launch_status();
 }
 
