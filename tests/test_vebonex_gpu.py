@@ -201,6 +201,29 @@ def test_greedy_generation_through_the_engine(tmp_path):
     assert eng.generate(prompts[:2], SamplingParams.greedy(max_tokens=n_new)) == want[:2]    # slots used before
 
 
+def test_command_line_with_random_weights_and_with_a_folder(tmp_path, capsys):
+    """``run --random-weights`` takes the design's config.json (the size that a folder gives by a tensor's shape is a
+    key then); sampling with a seed gives the same tokens twice; ``bench`` runs a folder."""
+    from inferrs_b200 import cli
+    path = str(tmp_path / "config.json")
+    with open(path, "w") as f:
+        json.dump(dict(CASE_P, eos_token_id=5), f)
+    common = [path, "--random-weights", "4", "--max-blocks", "32", "--max-batch-size", "2", "--max-tokens", "7",
+              "--ignore-eos", "--seed", "3", "--prefill-chunk", "16", "--random-prompt", "45"]
+    outs = []
+    for _ in range(2):
+        assert cli.main(["run"] + common + ["--temperature", "0.8", "--top-k", "20", "--dtype", "bf16"]) == 0
+        cap = capsys.readouterr()
+        outs.append([int(t) for t in cap.out.split()])
+        assert "45 prompt tokens, 7 generated" in cap.err
+    assert outs[0] == outs[1] and len(outs[0]) == 7 and all(0 <= t < CASE_P["vocab"] for t in outs[0])
+    folder = write_folder(str(tmp_path / "m"), CASE_Q, make_weights(CASE_Q, 5))
+    assert cli.main(["bench", folder, "--prompt-len", "30", "--max-tokens", "6", "--runs", "2", "--warmup", "1",
+                     "--max-blocks", "32", "--max-batch-size", "2", "--temperature", "0"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["prompt_len"] == 30 and out["prefill_tok_s"] > 0 and out["decode_tok_s"] > 0
+
+
 def test_trace_replay_of_a_folder(tmp_path):
     case, w = CASE_R, make_weights(CASE_R, 41)
     folder = write_folder(str(tmp_path / "m"), case, w)
