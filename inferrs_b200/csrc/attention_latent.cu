@@ -208,38 +208,55 @@ __device__ __forceinline__ void lm_cp_async16(void* dst, const void* src, int sr
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(d), "l"(src), "r"(src_bytes) : "memory");
 }
 
-template <int NT>   // n-tiles of 8 columns per warp in the second product: R = 32 * NT
+// NT: n-tiles of 8 columns per warp in the second product, R = 32 * NT.  TT: tokens per block.  TT = 1: a block per
+// row (blockIdx.x), any slices.  TT = 2: a block per tile of up to two tokens of one request, named by a tile list
+// (tile_req[i] < 0: no tile); the two tokens' queries meet every tile of latents together, so a prompt's latents
+// cross from L2 half as often and every B operand serves twice as many products.  One slice then.
+template <int NT, int TT>
 __global__ void __launch_bounds__(128)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long q_row, long q_head,
                             const __nv_bfloat16* __restrict__ plane, const int* __restrict__ block_table, int max_pages,
                             int page_size, int n_pages, const int* __restrict__ row_request,
-                            const int* __restrict__ positions, int n_heads, float scale, int window, int n_slices,
-                            __nv_bfloat16* __restrict__ out, long o_row, long o_head, float* __restrict__ ws_acc,
-                            float* __restrict__ ws_ml) {
-    constexpr int R = 32 * NT, LDC = R + LM_PAD, LDP = LM_KEYS + LM_PAD;
+                            const int* __restrict__ positions, const int* __restrict__ tile_req,
+                            const int* __restrict__ tile_row0, const int* __restrict__ q_start, int n_heads, float scale,
+                            int window, int n_slices, __nv_bfloat16* __restrict__ out, long o_row, long o_head,
+                            float* __restrict__ ws_acc, float* __restrict__ ws_ml) {
+    constexpr int R = 32 * NT, LDC = R + LM_PAD, LDP = LM_KEYS + LM_PAD, MR = TT * LM_ROWS;
     extern __shared__ __align__(16) unsigned char lm_smem[];
-    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [16][LDC]
-    __nv_bfloat16* c_s = q_s + LM_ROWS * LDC;                                // [64][LDC]
-    __nv_bfloat16* p_s = c_s + LM_KEYS * LDC;                                // [16][LDP]
-    float* pmax = reinterpret_cast<float*>(p_s + LM_ROWS * LDP);             // [4][16]
-    float* psum = pmax + 4 * LM_ROWS;                                        // [4][16]
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [TT * 16][LDC]
+    __nv_bfloat16* c_s = q_s + MR * LDC;                                     // [64][LDC]
+    __nv_bfloat16* p_s = c_s + LM_KEYS * LDC;                                // [TT * 16][LDP]
+    float* pmax = reinterpret_cast<float*>(p_s + MR * LDP);                  // [4][TT * 16]
+    float* psum = pmax + 4 * MR;                                             // [4][TT * 16]
     ib_grid_dependency_sync();
-    const int row = blockIdx.x, slice = blockIdx.z, head0 = blockIdx.y * LM_ROWS;
+    const int slice = blockIdx.z, head0 = blockIdx.y * LM_ROWS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pos = positions[row];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int* bt = block_table + (long)row_request[row] * max_pages;
-    const int first = (lo / LM_KEYS) * LM_KEYS;
-    const int n_tiles = (pos - first) / LM_KEYS + 1;
+    int row, req, n_tok = 1;
+    if (TT == 1) {
+        row = blockIdx.x;
+        req = row_request[row];
+    } else {
+        req = tile_req[blockIdx.x];
+        if (req < 0) return;                      // a place of the list without a tile (the whole block leaves)
+        row = tile_row0[blockIdx.x];
+        n_tok = min(TT, q_start[req + 1] - row);
+    }
+    const int pos0 = positions[row];              // the tokens of a tile stand at pos0, pos0 + 1, ...
+    const int pos_last = pos0 + n_tok - 1;
+    const int lo0 = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int* bt = block_table + (long)req * max_pages;
+    const int first = (lo0 / LM_KEYS) * LM_KEYS;
+    const int n_tiles = (pos_last - first) / LM_KEYS + 1;
     const int per_slice = (n_tiles + n_slices - 1) / n_slices;
     const int t0 = slice * per_slice, t1 = min(n_tiles, t0 + per_slice);
 
-    // the queries of the group's heads (rows of heads that do not exist are zeros)
-    for (int i = threadIdx.x; i < LM_ROWS * (R / 8); i += blockDim.x) {
+    // the queries of the group's heads (rows of heads and tokens that do not exist are zeros)
+    for (int i = threadIdx.x; i < MR * (R / 8); i += blockDim.x) {
         const int m = i / (R / 8), ch = i % (R / 8);
-        const int h = head0 + m;
-        const __nv_bfloat16* src = q + (long)row * q_row + (long)min(h, n_heads - 1) * q_head + ch * 8;
-        lm_cp_async16(q_s + m * LDC + ch * 8, src, h < n_heads ? 16 : 0);
+        const int tok = m / LM_ROWS, h = head0 + m % LM_ROWS;
+        const bool ok = h < n_heads && tok < n_tok;
+        const __nv_bfloat16* src = q + (long)(row + (ok ? tok : 0)) * q_row + (long)min(h, n_heads - 1) * q_head + ch * 8;
+        lm_cp_async16(q_s + m * LDC + ch * 8, src, ok ? 16 : 0);
     }
     // two threads per key: the page is looked up once per key and tile, each thread copies half of the latent
     auto load_tile = [&](int t) {
@@ -247,7 +264,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long q_row, lon
         const int j = first + t * LM_KEYS + jj;
         const __nv_bfloat16* src = plane;
         int bytes = 0;
-        if (j >= lo && j <= pos) {
+        if (j >= lo0 && j <= pos_last) {
             const int page = bt[j / page_size];
             if (page >= 0 && page < n_pages) {
                 src = plane + ((long)page * page_size + (j % page_size)) * R;
@@ -261,115 +278,139 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long q_row, lon
     if (t0 < t1) load_tile(t0);
     asm volatile("cp.async.commit_group;" ::: "memory");
 
-    float o[NT][4];
+    float o[TT][NT][4];
+    float m_run[TT][2], l_run[TT][2];                 // rows lane/4 and lane/4 + 8 of every token
 #pragma unroll
-    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};     // rows lane/4 and lane/4 + 8
+    for (int tk = 0; tk < TT; ++tk) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i) o[tk][i][0] = o[tk][i][1] = o[tk][i][2] = o[tk][i][3] = 0.0f;
+        m_run[tk][0] = m_run[tk][1] = -INFINITY;
+        l_run[tk][0] = l_run[tk][1] = 0.0f;
+    }
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
 
     for (int t = t0; t < t1; ++t) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         const __nv_bfloat16* ct = c_s;
-        // ---- scores of this warp's 16 keys ------------------------------------------------------------------
+        // ---- scores of this warp's 16 keys, for every token -------------------------------------------------
         // (two sets of accumulators take turns, so that a product does not wait for the one before it)
-        float sc[2][4], sd[2][4];
+        float sc[TT][2][4], sd[TT][2][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
-            sd[i][0] = sd[i][1] = sd[i][2] = sd[i][3] = 0.0f;
-        }
+        for (int tk = 0; tk < TT; ++tk)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                sc[tk][i][0] = sc[tk][i][1] = sc[tk][i][2] = sc[tk][i][3] = 0.0f;
+                sd[tk][i][0] = sd[tk][i][1] = sd[tk][i][2] = sd[tk][i][3] = 0.0f;
+            }
 #pragma unroll
         for (int ks = 0; ks < R / 16; ++ks) {
-            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-            lm_ldmatrix_x4(a0, a1, a2, a3, q_s + (lane & 15) * LDC + ks * 16 + (lane >> 4) * 8);
+            uint32_t b0, b1, b2, b3;
             lm_ldmatrix_x4(b0, b1, b2, b3, ct + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * LDC + ks * 16 + ((lane >> 3) & 1) * 8);
-            if (ks & 1) {
-                lm_mma(sd[0], a0, a1, a2, a3, b0, b1);
-                lm_mma(sd[1], a0, a1, a2, a3, b2, b3);
-            } else {
-                lm_mma(sc[0], a0, a1, a2, a3, b0, b1);
-                lm_mma(sc[1], a0, a1, a2, a3, b2, b3);
+#pragma unroll
+            for (int tk = 0; tk < TT; ++tk) {
+                uint32_t a0, a1, a2, a3;
+                lm_ldmatrix_x4(a0, a1, a2, a3, q_s + (tk * LM_ROWS + (lane & 15)) * LDC + ks * 16 + (lane >> 4) * 8);
+                if (ks & 1) {
+                    lm_mma(sd[tk][0], a0, a1, a2, a3, b0, b1);
+                    lm_mma(sd[tk][1], a0, a1, a2, a3, b2, b3);
+                } else {
+                    lm_mma(sc[tk][0], a0, a1, a2, a3, b0, b1);
+                    lm_mma(sc[tk][1], a0, a1, a2, a3, b2, b3);
+                }
             }
         }
-#pragma unroll
-        for (int i = 0; i < 2; ++i)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) sc[i][c] += sd[i][c];
         const int j_base = first + t * LM_KEYS + warp * 16 + 2 * (lane & 3);
-        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
+        for (int tk = 0; tk < TT; ++tk) {
+            const int lo = lo0 + (window > 0 && pos0 + tk - window + 1 > 0 ? (pos0 + tk - window + 1) - lo0 : 0);
+            const int hi = tk < n_tok ? pos0 + tk : -1;             // a token that does not exist sees nothing
+            float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int j = j_base + i * 8 + (c & 1);
-                const float v = (j >= lo && j <= pos) ? sc[i][c] * scale : -INFINITY;
-                sc[i][c] = v;
-                mx[c >> 1] = fmaxf(mx[c >> 1], v);
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int j = j_base + i * 8 + (c & 1);
+                    const float v = (j >= lo && j <= hi) ? (sc[tk][i][c] + sd[tk][i][c]) * scale : -INFINITY;
+                    sc[tk][i][c] = v;
+                    mx[c >> 1] = fmaxf(mx[c >> 1], v);
+                }
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 1));
+                mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 2));
             }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 1));
-            mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 2));
-        }
-        if ((lane & 3) == 0) {
-            pmax[warp * LM_ROWS + r_lo] = mx[0];
-            pmax[warp * LM_ROWS + r_hi] = mx[1];
+            if ((lane & 3) == 0) {
+                pmax[warp * MR + tk * LM_ROWS + r_lo] = mx[0];
+                pmax[warp * MR + tk * LM_ROWS + r_hi] = mx[1];
+            }
         }
         __syncthreads();
-        float m_new[2], corr[2];
+        float corr[TT][2];
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int rr = k ? r_hi : r_lo;
-            const float tm = fmaxf(fmaxf(pmax[rr], pmax[LM_ROWS + rr]), fmaxf(pmax[2 * LM_ROWS + rr], pmax[3 * LM_ROWS + rr]));
-            m_new[k] = fmaxf(m_run[k], tm);
-            corr[k] = (m_run[k] == -INFINITY) ? 0.0f : expf(m_run[k] - m_new[k]);
-        }
-        float sm[2] = {0.0f, 0.0f};
+        for (int tk = 0; tk < TT; ++tk) {
+            float m_new[2];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            float p[4];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                p[c] = (sc[i][c] == -INFINITY) ? 0.0f : expf(sc[i][c] - m_new[c >> 1]);
-                sm[c >> 1] += p[c];
+            for (int k = 0; k < 2; ++k) {
+                const int rr = tk * LM_ROWS + (k ? r_hi : r_lo);
+                const float tm = fmaxf(fmaxf(pmax[rr], pmax[MR + rr]), fmaxf(pmax[2 * MR + rr], pmax[3 * MR + rr]));
+                m_new[k] = fmaxf(m_run[tk][k], tm);
+                corr[tk][k] = (m_run[tk][k] == -INFINITY) ? 0.0f : expf(m_run[tk][k] - m_new[k]);
+                m_run[tk][k] = m_new[k];
             }
-            const int col = warp * 16 + i * 8 + 2 * (lane & 3);
-            *reinterpret_cast<__nv_bfloat162*>(p_s + r_lo * LDP + col) = __floats2bfloat162_rn(p[0], p[1]);
-            *reinterpret_cast<__nv_bfloat162*>(p_s + r_hi * LDP + col) = __floats2bfloat162_rn(p[2], p[3]);
-        }
+            float sm[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            sm[k] += __shfl_xor_sync(0xffffffffu, sm[k], 1);
-            sm[k] += __shfl_xor_sync(0xffffffffu, sm[k], 2);
-        }
-        if ((lane & 3) == 0) {
-            psum[warp * LM_ROWS + r_lo] = sm[0];
-            psum[warp * LM_ROWS + r_hi] = sm[1];
+            for (int i = 0; i < 2; ++i) {
+                float p[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    p[c] = (sc[tk][i][c] == -INFINITY) ? 0.0f : expf(sc[tk][i][c] - m_new[c >> 1]);
+                    sm[c >> 1] += p[c];
+                }
+                const int col = warp * 16 + i * 8 + 2 * (lane & 3);
+                *reinterpret_cast<__nv_bfloat162*>(p_s + (tk * LM_ROWS + r_lo) * LDP + col) = __floats2bfloat162_rn(p[0], p[1]);
+                *reinterpret_cast<__nv_bfloat162*>(p_s + (tk * LM_ROWS + r_hi) * LDP + col) = __floats2bfloat162_rn(p[2], p[3]);
+            }
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                sm[k] += __shfl_xor_sync(0xffffffffu, sm[k], 1);
+                sm[k] += __shfl_xor_sync(0xffffffffu, sm[k], 2);
+            }
+            if ((lane & 3) == 0) {
+                psum[warp * MR + tk * LM_ROWS + r_lo] = sm[0];
+                psum[warp * MR + tk * LM_ROWS + r_hi] = sm[1];
+            }
         }
         __syncthreads();
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int rr = k ? r_hi : r_lo;
-            l_run[k] = l_run[k] * corr[k] + ((psum[rr] + psum[LM_ROWS + rr]) + (psum[2 * LM_ROWS + rr] + psum[3 * LM_ROWS + rr]));
-            m_run[k] = m_new[k];
-        }
-        // ---- this warp's quarter of the sums over all 64 keys ------------------------------------------------
+        for (int tk = 0; tk < TT; ++tk) {
 #pragma unroll
-        for (int i = 0; i < NT; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            for (int k = 0; k < 2; ++k) {
+                const int rr = tk * LM_ROWS + (k ? r_hi : r_lo);
+                l_run[tk][k] = l_run[tk][k] * corr[tk][k] + ((psum[rr] + psum[MR + rr]) + (psum[2 * MR + rr] + psum[3 * MR + rr]));
+            }
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                o[tk][i][0] *= corr[tk][0]; o[tk][i][1] *= corr[tk][0];
+                o[tk][i][2] *= corr[tk][1]; o[tk][i][3] *= corr[tk][1];
+            }
         }
+        // ---- this warp's quarter of the sums over all 64 keys, for every token -------------------------------
 #pragma unroll
         for (int kk = 0; kk < LM_KEYS / 16; ++kk) {
-            uint32_t a0, a1, a2, a3;
-            lm_ldmatrix_x4(a0, a1, a2, a3, p_s + (lane & 15) * LDP + kk * 16 + (lane >> 4) * 8);
+            uint32_t a[TT][4];
+#pragma unroll
+            for (int tk = 0; tk < TT; ++tk)
+                lm_ldmatrix_x4(a[tk][0], a[tk][1], a[tk][2], a[tk][3], p_s + (tk * LM_ROWS + (lane & 15)) * LDP + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int i = 0; i < NT; i += 2) {
                 uint32_t b0, b1, b2, b3;
                 lm_ldmatrix_x4_trans(b0, b1, b2, b3, ct + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDC + warp * (R / 4) + i * 8 + (lane >> 4) * 8);
-                lm_mma(o[i], a0, a1, a2, a3, b0, b1);
-                if (i + 1 < NT) lm_mma(o[i + 1], a0, a1, a2, a3, b2, b3);   // an odd last tile: the other half read padding
+#pragma unroll
+                for (int tk = 0; tk < TT; ++tk) {
+                    lm_mma(o[tk][i], a[tk][0], a[tk][1], a[tk][2], a[tk][3], b0, b1);
+                    if (i + 1 < NT) lm_mma(o[tk][i + 1], a[tk][0], a[tk][1], a[tk][2], a[tk][3], b2, b3);   // an odd last tile: the other half read padding
+                }
             }
         }
         __syncthreads();      // the buffer, P and the maxima are free for the next tile
@@ -379,48 +420,54 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long q_row, lon
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     // ---- out ------------------------------------------------------------------------------------------------
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        const int h = head0 + (k ? r_hi : r_lo);
-        if (h >= n_heads) continue;
-        if (n_slices == 1) {
-            const float inv = l_run[k] > 0.0f ? 1.0f / l_run[k] : 0.0f;
-            __nv_bfloat16* dst = out + (long)row * o_row + (long)h * o_head + warp * (R / 4) + 2 * (lane & 3);
+    for (int tk = 0; tk < TT; ++tk) {
+        if (tk >= n_tok) continue;
 #pragma unroll
-            for (int i = 0; i < NT; ++i)
-                *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = __floats2bfloat162_rn(o[i][2 * k] * inv, o[i][2 * k + 1] * inv);
-        } else {
-            const long item = ((long)row * n_heads + h) * n_slices + slice;
-            float* dst = ws_acc + item * R + warp * (R / 4) + 2 * (lane & 3);
+        for (int k = 0; k < 2; ++k) {
+            const int h = head0 + (k ? r_hi : r_lo);
+            if (h >= n_heads) continue;
+            if (n_slices == 1) {
+                const float inv = l_run[tk][k] > 0.0f ? 1.0f / l_run[tk][k] : 0.0f;
+                __nv_bfloat16* dst = out + (long)(row + tk) * o_row + (long)h * o_head + warp * (R / 4) + 2 * (lane & 3);
 #pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                dst[i * 8] = o[i][2 * k];
-                dst[i * 8 + 1] = o[i][2 * k + 1];
-            }
-            if (warp == 0 && (lane & 3) == 0) {
-                ws_ml[item * 2] = m_run[k];
-                ws_ml[item * 2 + 1] = l_run[k];
+                for (int i = 0; i < NT; ++i)
+                    *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) =
+                        __floats2bfloat162_rn(o[tk][i][2 * k] * inv, o[tk][i][2 * k + 1] * inv);
+            } else {
+                const long item = ((long)(row + tk) * n_heads + h) * n_slices + slice;
+                float* dst = ws_acc + item * R + warp * (R / 4) + 2 * (lane & 3);
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    dst[i * 8] = o[tk][i][2 * k];
+                    dst[i * 8 + 1] = o[tk][i][2 * k + 1];
+                }
+                if (warp == 0 && (lane & 3) == 0) {
+                    ws_ml[item * 2] = m_run[tk][k];
+                    ws_ml[item * 2 + 1] = l_run[tk][k];
+                }
             }
         }
     }
 }
 
-static IbDeviceSet latent_mma_smem_set[17];
+static IbDeviceSet latent_mma_smem_set[2][17];
 
-template <int NT>
+template <int NT, int TT>
 static int launch_latent_mma(const void* q, long q_row, long q_head, const void* plane, const int* block_table,
                              int max_pages, int page_size, int n_pages, const int* row_request, const int* positions,
-                             int n_rows, int n_heads, float scale, int window, int n_slices, void* out, long o_row,
-                             long o_head, float* ws_acc, float* ws_ml, cudaStream_t stream) {
-    constexpr int R = 32 * NT, LDC = R + LM_PAD, LDP = LM_KEYS + LM_PAD;
-    const size_t smem = (size_t)(LM_ROWS * LDC + LM_KEYS * LDC + LM_ROWS * LDP) * 2 + 8 * LM_ROWS * sizeof(float);
+                             const int* tile_req, const int* tile_row0, const int* q_start, int n_blocks, int n_heads,
+                             float scale, int window, int n_slices, void* out, long o_row, long o_head, float* ws_acc,
+                             float* ws_ml, cudaStream_t stream) {
+    constexpr int R = 32 * NT, LDC = R + LM_PAD, LDP = LM_KEYS + LM_PAD, MR = TT * LM_ROWS;
+    const size_t smem = (size_t)(MR * LDC + LM_KEYS * LDC + MR * LDP) * 2 + 8 * MR * sizeof(float);
     if (smem > 48 * 1024) {
-        const int e = ib_allow_dynamic_smem(latent_mma_smem_set[NT], latent_attention_mma_kernel<NT>, smem);
+        const int e = ib_allow_dynamic_smem(latent_mma_smem_set[TT - 1][NT], latent_attention_mma_kernel<NT, TT>, smem);
         if (e != IB_OK) return e;
     }
-    const dim3 grid(n_rows, (n_heads + LM_ROWS - 1) / LM_ROWS, n_slices);
-    ib_launch(latent_attention_mma_kernel<NT>, grid, 128, smem, stream, (const __nv_bfloat16*)q, q_row, q_head,
-              (const __nv_bfloat16*)plane, block_table, max_pages, page_size, n_pages, row_request, positions, n_heads,
-              scale, window, n_slices, (__nv_bfloat16*)out, o_row, o_head, ws_acc, ws_ml);
+    const dim3 grid(n_blocks, (n_heads + LM_ROWS - 1) / LM_ROWS, n_slices);
+    ib_launch(latent_attention_mma_kernel<NT, TT>, grid, 128, smem, stream, (const __nv_bfloat16*)q, q_row, q_head,
+              (const __nv_bfloat16*)plane, block_table, max_pages, page_size, n_pages, row_request, positions, tile_req,
+              tile_row0, q_start, n_heads, scale, window, n_slices, (__nv_bfloat16*)out, o_row, o_head, ws_acc, ws_ml);
     return ib_launch_status();
 }
 #endif  // IB_ACT_BF16
@@ -448,12 +495,14 @@ static int launch_latent(IbDeviceSet& set, const void* q, long q_row, long q_hea
 
 // q: element (row, h, e) at q[row * q_row + h * q_head + e], float (q_is_f32) or act_t; out likewise, act_t.
 // plane [n_pages, page_size, R] act_t.  n_slices > 1 needs ws_acc [rows * heads * n_slices * R] and
-// ws_ml [rows * heads * n_slices * 2] floats.
+// ws_ml [rows * heads * n_slices * 2] floats.  tile_req, tile_row0 [n_tiles] and q_start (or null): the step's rows
+// cut into tiles of up to two tokens of one request each; the tensor-core form then takes two tokens per block.
 IB_EXPORT int ib_latent_attention(const void* q, int q_is_f32, long q_row, long q_head, const void* plane,
                                   const int* block_table, int max_pages, int page_size, int n_pages,
                                   const int* row_request, const int* positions, int n_rows, int n_heads, int R,
                                   float scale, int window, int n_slices, void* out, long o_row, long o_head,
-                                  float* ws_acc, float* ws_ml, cudaStream_t stream) {
+                                  float* ws_acc, float* ws_ml, const int* tile_req, const int* tile_row0,
+                                  const int* q_start, int n_tiles, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (n_heads <= 0 || R <= 0 || page_size <= 0 || max_pages <= 0 || n_slices <= 0 || n_slices > 64 ||
         (n_slices > 1 && (ws_acc == nullptr || ws_ml == nullptr)))
@@ -463,11 +512,18 @@ IB_EXPORT int ib_latent_attention(const void* q, int q_is_f32, long q_row, long 
 #if IB_ACT_BF16
     // bfloat16 queries and latents of a multiple of 32 numbers: the tensor cores
     if (!q_is_f32 && R % 32 == 0 && page_size > 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)plane % 16) == 0) {
+        // a list of tiles of up to two tokens (prompt portions, one slice): two tokens per block
+        const bool pairs = tile_req != nullptr && tile_row0 != nullptr && q_start != nullptr && n_tiles > 0 && n_slices == 1;
         switch (R / 32) {
 #define IB_LATM(NT)                                                                                                  \
-        case NT: e = launch_latent_mma<NT>(q, q_row, q_head, plane, block_table, max_pages, page_size, n_pages,      \
-                                           row_request, positions, n_rows, n_heads, scale, window, n_slices, out,   \
-                                           o_row, o_head, ws_acc, ws_ml, stream); break;
+        case NT:                                                                                                     \
+            e = pairs ? launch_latent_mma<NT, 2>(q, q_row, q_head, plane, block_table, max_pages, page_size, n_pages, \
+                                                 row_request, positions, tile_req, tile_row0, q_start, n_tiles,      \
+                                                 n_heads, scale, window, 1, out, o_row, o_head, ws_acc, ws_ml, stream) \
+                      : launch_latent_mma<NT, 1>(q, q_row, q_head, plane, block_table, max_pages, page_size, n_pages, \
+                                                 row_request, positions, nullptr, nullptr, nullptr, n_rows, n_heads, \
+                                                 scale, window, n_slices, out, o_row, o_head, ws_acc, ws_ml, stream); \
+            break;
             IB_LATM(1) IB_LATM(2) IB_LATM(3) IB_LATM(4) IB_LATM(5) IB_LATM(6) IB_LATM(7) IB_LATM(8) IB_LATM(9)
             IB_LATM(10) IB_LATM(11) IB_LATM(12) IB_LATM(13) IB_LATM(14) IB_LATM(15) IB_LATM(16)
 #undef IB_LATM

@@ -76,7 +76,7 @@ _SIGNATURES = {
                        c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ib_latent_attention": [c_void_p, c_int, c_long, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_long, c_long, c_void_p, c_void_p,
-                            c_void_p],
+                            c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "ib_gemm_tn_simt_batched": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
                                 c_long, c_int, c_long, c_long, c_long, c_void_p],
     "ib_sample": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -344,6 +344,7 @@ def linear_scan(mode: int, proj: torch.Tensor, q_col: int, k_col: int, v_col: in
         heads, d_dim, e_dim, int(max_rows), _stream()), "linear_scan")
 
 
+LATENT_TILE_TOKENS = 2      # tokens of a prompt portion that one block of the tensor-core form takes
 LATENT_SLICE_KEYS = 128     # fewest keys per slice when a row's keys are cut over several blocks
 LATENT_RESIDENT_BLOCKS = 296   # two blocks of the tensor-core form per SM
 
@@ -360,10 +361,14 @@ def latent_slices(n_rows: int, n_heads: int, max_kv_len: int) -> int:
 
 
 def latent_attention(q: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor, row_request: torch.Tensor,
-                     positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor, n_slices: int = 1):
+                     positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor, n_slices: int = 1,
+                     tiles=None):
     """Attention of every row over its request's cached latents, which serve every head as key and as value:
     out[h, r] = sum_j softmax_j(scale * q[h, r] . c_j) c_j over the visible j.  ``q`` and ``out`` are head-major
-    [H, rows, R] (float32 or the activation dtype; the activation dtype), ``plane`` [pages, page_size, R]."""
+    [H, rows, R] (float32 or the activation dtype; the activation dtype), ``plane`` [pages, page_size, R].
+    ``tiles`` = (tile_req, tile_row0, n_tiles, q_start): the step's rows cut into tiles of up to ``LATENT_TILE_TOKENS``
+    tokens of one request each (``StepContext.attention_tiles``; -1 marks a place without a tile); with one slice the
+    tensor-core form then takes a tile per block."""
     act = out.dtype
     _need(q, "q", (torch.float32, act), 3)
     _need(out, "out", _W, 3)
@@ -384,7 +389,9 @@ def latent_attention(q: torch.Tensor, plane: torch.Tensor, block_table: torch.Te
     _check(_core(act).ib_latent_attention(
         _p(q), int(q.dtype == torch.float32), rank, n * rank, _p(plane), _p(block_table), block_table.shape[1],
         page_size, n_pages, _p(row_request), _p(positions), n, heads, rank, float(scale), int(window) if window else 0,
-        int(n_slices), _p(out), rank, n * rank, _p(ws_acc), _p(ws_ml), _stream()), "latent_attention")
+        int(n_slices), _p(out), rank, n * rank, _p(ws_acc), _p(ws_ml),
+        *((_p(tiles[0]), _p(tiles[1]), _p(tiles[3]), int(tiles[2])) if tiles is not None and n_slices == 1
+          else (None, None, None, 0)), _stream()), "latent_attention")
     if n_slices > 1:
         count_launches(1)
 

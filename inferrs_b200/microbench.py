@@ -197,7 +197,12 @@ def latent(args) -> dict:
     out = torch.empty(h, n, r, dtype=dtype, device=dev)
     slices = args.slices or kernels.latent_slices(n, h, max(lens))
     table = table.to(dev)
-    fn = lambda: kernels.latent_attention(q, plane, table, row_request, positions, r ** -0.5, None, out, slices)  # noqa: E731
+    tiles = None
+    if args.form == "prefill" and slices == 1:     # as the engine runs prompt portions: two tokens of the request per block
+        tt = kernels.LATENT_TILE_TOKENS
+        row0 = torch.arange(0, n, tt, dtype=torch.int32, device=dev)
+        tiles = (torch.zeros_like(row0), row0, row0.shape[0], torch.tensor([0, n], dtype=torch.int32, device=dev))
+    fn = lambda: kernels.latent_attention(q, plane, table, row_request, positions, r ** -0.5, None, out, slices, tiles)  # noqa: E731
     us = _time(fn, args.iters)
     el = 4 if dtype == torch.float32 else 2
     pairs = sum(t * (c - t) + t * (t + 1) // 2 for c, t in zip(lens, new))

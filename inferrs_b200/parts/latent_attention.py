@@ -91,8 +91,14 @@ class LatentAttention:
         kernels.batched_linear(q.view(n, h, s.key_dim).transpose(0, 1), self.uk_t, q_lat, act)
         mixed = torch.empty_like(q_lat)
         rows_for_dispatch = ctx.extra.get("dispatch_rows", ctx.n_rows)
-        kernels.latent_attention(q_lat, plane, table, ctx.row_request, ctx.positions, s.scale, s.window, mixed,
-                                 kernels.latent_slices(rows_for_dispatch, h, ctx.max_kv_len))
+        n_slices = kernels.latent_slices(rows_for_dispatch, h, ctx.max_kv_len)
+        tiles = None
+        if not ctx.decode_only and n_slices == 1 and act == torch.bfloat16 and s.kv_rank % 32 == 0:
+            # prompt portions: two tokens of a request per block (the kernel's tensor-core form)
+            tile_req, tile_row0, n_tiles = ctx.attention_tiles(kernels.LATENT_TILE_TOKENS)
+            tiles = (tile_req, tile_row0, n_tiles, ctx.q_start)
+        kernels.latent_attention(q_lat, plane, table, ctx.row_request, ctx.positions, s.scale, s.window, mixed, n_slices,
+                                 tiles)
         heads = torch.empty((h, n, s.value_dim), dtype=act, device=dev)
         kernels.batched_linear(mixed, self.uv, heads, act)
         gated = torch.empty((n, h * s.value_dim), dtype=act, device=dev)

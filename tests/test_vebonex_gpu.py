@@ -135,7 +135,7 @@ def test_unequal_requests_in_one_batch_slots_and_pages_used_again(name, dtype):
     runner.manager.check_invariants()
 
 
-@pytest.mark.parametrize("name", ["P", "Q"])
+@pytest.mark.parametrize("name", ["P", "Q", "R"])
 def test_replayed_steps_give_what_plain_launches_give(name):
     """The same requests through steps captured as CUDA graphs (padding requests, the spare state slot) and through
     steps launched kernel by kernel."""
@@ -425,7 +425,7 @@ def paged_latents(c_per_request, page_size, n_pages, dtype, seed):
                                                 (1, 512, 100, 3), (17, 24, None, 7),
                                                 # ranks that the tensor-core form of the bfloat16 build takes
                                                 (6, 96, None, 1), (16, 128, None, 1), (3, 64, 40, 2), (40, 256, None, 3),
-                                                (33, 32, 70, 5), (16, 512, None, 2)])
+                                                (33, 32, 70, 5), (16, 512, None, 2), (5, 64, 33, 1), (16, 512, None, 1)])
 def test_latent_attention_kernel(H, R, window, slices, dtype):
     """A portion of one request (its later tokens are in the cache already and must stay unseen), a single token of
     another with many keys, and a first token; shuffled pages."""
@@ -441,14 +441,26 @@ def test_latent_attention_kernel(H, R, window, slices, dtype):
     n = len(positions)
     q_lat = (torch.randn(H, n, R, generator=g) * 1.5).to(dtype).float()
     scale = 0.6 / R ** 0.5
-    out = torch.empty((H, n, R), dtype=dtype, device="cuda")
-    kernels.latent_attention(act(q_lat, dtype), plane, table, torch.tensor(row_request, dtype=torch.int32, device="cuda"),
-                             torch.tensor(positions, dtype=torch.int32, device="cuda"), scale, window, out, slices)
-    at = 0
+    # once row by row, once (one slice) with the rows cut into tiles of two tokens of one request, one place of the
+    # list empty: the form that prompt portions take on the tensor cores
+    tile_req, tile_row0, starts = [], [], [0]
     for r, rows in enumerate(rows_of):
-        want = latent_mix(q_lat[:, at:at + len(rows)], c[r], scale, rows, window)
-        assert rel_err(out[:, at:at + len(rows)], want) < (2e-5 if dtype == torch.float32 else 2e-2), r
-        at += len(rows)
+        tile_req += [r] * ((len(rows) + 1) // 2)
+        tile_row0 += list(range(starts[-1], starts[-1] + len(rows), 2))
+        starts.append(starts[-1] + len(rows))
+    tile_req.insert(3, -1)
+    tile_row0.insert(3, 0)
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    tiles = (dev(tile_req), dev(tile_row0), len(tile_req), dev(starts))
+    for use_tiles in ([False, True] if slices == 1 else [False]):
+        out = torch.full((H, n, R), float("nan"), dtype=dtype, device="cuda")
+        kernels.latent_attention(act(q_lat, dtype), plane, table, dev(row_request), dev(positions), scale, window, out,
+                                 slices, tiles if use_tiles else None)
+        at = 0
+        for r, rows in enumerate(rows_of):
+            want = latent_mix(q_lat[:, at:at + len(rows)], c[r], scale, rows, window)
+            assert rel_err(out[:, at:at + len(rows)], want) < (2e-5 if dtype == torch.float32 else 2e-2), (r, use_tiles)
+            at += len(rows)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

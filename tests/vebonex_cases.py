@@ -43,13 +43,14 @@ CASE_Q = {
         {"type": "gla", "mixer": {"heads": 1, "dim": 16, "vdim": 64, "tau": 2.0, "a_rank": 4}, "mlp": _ff(48)},
     ],
 }
-# no hyper-connections (the plain residual), norms in two parts, many heads on one latent
+# no hyper-connections (the plain residual), norms in two parts, many heads on one latent whose size the tensor-core
+# form of the latent attention takes
 CASE_R = {
     "architecture": "Vebonex", "vocab": 130, "width": 128, "max_positions": 512,
     "norm": {"eps": 1e-5, "groups": 2},
     "layers": [
         {"type": "gla", "mixer": {"heads": 2, "dim": 64, "vdim": 64, "tau": 32.0, "a_rank": 16}, "mlp": _ff(192)},
-        {"type": "latent_attention", "mixer": _latent(18, 16, 8, 32, 48, 0.25), "mlp": _ff(192)},
+        {"type": "latent_attention", "mixer": _latent(18, 16, 8, 32, 64, 0.25), "mlp": _ff(192)},
     ],
 }
 CASES = {"P": CASE_P, "Q": CASE_Q, "R": CASE_R}
