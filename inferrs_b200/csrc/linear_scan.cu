@@ -36,7 +36,9 @@ __device__ __forceinline__ float ls_logsigmoid(float z) { return fminf(z, 0.0f) 
 
 // CH tokens per chunk: 16, or 1 for steps of single tokens (few registers, many blocks per SM).  MAXT: the most
 // threads of a block, 256 (up to 128 key channels) or 512 (up to 256): the registers must allow that many.
-template <int MODE, int CH, int MAXT>
+// COLS columns of S per block: 32 (a lane per column), or 16 where a step has too few (request, head, 32 columns) to
+// give every SM a block: the two halves of a warp then own the same 16 columns and eight rows each.
+template <int MODE, int CH, int MAXT, int COLS>
 __global__ void __launch_bounds__(MAXT)
 linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col, int v_col,
                                    const float* __restrict__ gates, long ld_gates, const float* __restrict__ gate_bias,
@@ -47,14 +49,16 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
     ib_grid_dependency_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int Dp = n_warps * LS_RW;                     // D rounded up: the rows beyond D hold zeros
-    const int h = blockIdx.y, r = blockIdx.z, e0 = blockIdx.x * LS_COLS, d0 = warp * LS_RW;
+    constexpr int HALVES = 32 / COLS, RL = LS_RW / HALVES;   // rows of S per lane
+    const int col = lane % COLS, half_w = lane / COLS, n_units = n_warps * HALVES;
+    const int h = blockIdx.y, r = blockIdx.z, e0 = blockIdx.x * COLS, d0 = warp * LS_RW, dl = d0 + half_w * RL;
     const int row0 = q_start[r], row1 = q_start[r + 1];
     if (row1 <= row0) return;                           // the whole block leaves
     float* q_s = smem;                                  // [CH][Dp]
     float* k_s = q_s + CH * Dp;                         // [CH][Dp]
     float* a_s = k_s + CH * Dp;                         // [CH][Dp]   mode 0: the decays
-    float* v_s = a_s + (MODE == 0 ? CH * Dp : 0);       // [CH][32]
-    float* part = v_s + CH * LS_COLS;                   // [CH][n_warps][32]
+    float* v_s = a_s + (MODE == 0 ? CH * Dp : 0);       // [CH][COLS]
+    float* part = v_s + CH * LS_COLS;                   // [CH][n_units][COLS]
     float* npart = part + CH * n_warps * LS_COLS;       // [CH][n_warps]     mode 1
     float* g_s = npart + CH * n_warps;                  // [3][CH]           mode 1: keep, take, exp(-m)
     float* m_s = g_s + 4 * CH;                          // [1]               mode 1: the running maximum
@@ -63,15 +67,15 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
     float* st_S = st + (long)h * D * E;
     float* st_n = st + (long)H * D * E + (long)h * D;
     float* st_m = st + (long)H * D * E + (long)H * D + h;
-    const bool col_ok = e0 + lane < E;
+    const bool col_ok = e0 + col < E;
 
     // the state's loads carry no condition (see the chunk's loads below): the address is brought inside
-    float S[LS_RW];
-    const int e_in = min(e0 + lane, E - 1);
+    float S[RL];
+    const int e_in = min(e0 + col, E - 1);
 #pragma unroll
-    for (int i = 0; i < LS_RW; ++i) S[i] = st_S[(long)min(d0 + i, D - 1) * E + e_in];
+    for (int i = 0; i < RL; ++i) S[i] = st_S[(long)min(dl + i, D - 1) * E + e_in];
 #pragma unroll
-    for (int i = 0; i < LS_RW; ++i) S[i] = (col_ok && d0 + i < D) ? S[i] : 0.0f;
+    for (int i = 0; i < RL; ++i) S[i] = (col_ok && dl + i < D) ? S[i] : 0.0f;
     const bool n_mine = lane < LS_RW && d0 + lane < D;  // mode 1: lanes 0..15 keep n of the rows d0 + lane
     float n_row = 0.0f;
     if (MODE == 1) {
@@ -105,8 +109,8 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
             rq[i] = p[q_col + h * D + d_in];
             rk[i] = p[k_col + h * D + d_in];
             if (MODE == 0) rg[i] = gates[(long)min(c0 + t, last_row) * ld_gates + h * D + d_in];
-            const int idx = threadIdx.x + i * blockDim.x;          // the values: [tokens][32 columns]
-            const int vt = min(idx >> 5, CH - 1), ve = min(e0 + (idx & 31), E - 1);
+            const int idx = threadIdx.x + i * blockDim.x;          // the values: [tokens][COLS columns]
+            const int vt = min(idx / COLS, CH - 1), ve = min(e0 + (idx % COLS), E - 1);
             rv[i] = proj[(long)min(c0 + vt, last_row) * ld + v_col + h * E + ve];
         }
         if (MODE == 1 && warp == 0) {
@@ -130,7 +134,7 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
                     a_s[t * Dp + d_mine] = d_ok ? expf(ls_logsigmoid(rg[i] + my_bias) * gate_param) : 1.0f;   // 1 / tau
             }
             const int idx = threadIdx.x + i * blockDim.x;
-            if (idx < nc * LS_COLS) v_s[idx] = (e0 + (idx & 31) < E) ? ib_to_float(rv[i]) : 0.0f;
+            if (idx < nc * COLS) v_s[idx] = (e0 + (idx % COLS) < E) ? ib_to_float(rv[i]) : 0.0f;
         }
         if (MODE == 1 && warp == 0) {
             const float cap = gate_param;
@@ -178,14 +182,14 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
         }
         // ---- the tokens, one after the other ----------------------------------------------------------------
         for (int t = 0; t < nc; ++t) {
-            const float vt = MODE == 1 ? v_s[t * LS_COLS + lane] * g_s[CH + t] : v_s[t * LS_COLS + lane];   // v times exp(i - m)
-            const float4* q4 = reinterpret_cast<const float4*>(q_s + t * Dp + d0);
-            const float4* k4 = reinterpret_cast<const float4*>(k_s + t * Dp + d0);
-            const float4* a4 = reinterpret_cast<const float4*>(a_s + t * Dp + d0);
+            const float vt = MODE == 1 ? v_s[t * COLS + col] * g_s[CH + t] : v_s[t * COLS + col];   // v times exp(i - m)
+            const float4* q4 = reinterpret_cast<const float4*>(q_s + t * Dp + dl);
+            const float4* k4 = reinterpret_cast<const float4*>(k_s + t * Dp + dl);
+            const float4* a4 = reinterpret_cast<const float4*>(a_s + t * Dp + dl);
             const float keep = MODE == 1 ? g_s[t] : 0.0f;
             float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < LS_RW / 4; ++i) {
+            for (int i = 0; i < RL / 4; ++i) {
                 const float4 q = q4[i], k = k4[i];
                 float4 a;
                 if (MODE == 0) a = a4[i]; else a = make_float4(keep, keep, keep, keep);
@@ -194,14 +198,14 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
                 S[4 * i + 2] = fmaf(a.z, S[4 * i + 2], k.z * vt); acc2 = fmaf(S[4 * i + 2], q.z, acc2);
                 S[4 * i + 3] = fmaf(a.w, S[4 * i + 3], k.w * vt); acc3 = fmaf(S[4 * i + 3], q.w, acc3);
             }
-            part[(t * n_warps + warp) * LS_COLS + lane] = (acc0 + acc1) + (acc2 + acc3);
+            part[(t * n_units + warp * HALVES + half_w) * COLS + col] = (acc0 + acc1) + (acc2 + acc3);
         }
         __syncthreads();
         // ---- the warps' shares of every token's product, summed ---------------------------------------------
-        for (int idx = threadIdx.x; idx < nc * LS_COLS; idx += blockDim.x) {
-            const int t = idx >> 5, e = idx & 31;
+        for (int idx = threadIdx.x; idx < nc * COLS; idx += blockDim.x) {
+            const int t = idx / COLS, e = idx % COLS;
             float o = 0.0f;
-            for (int w = 0; w < n_warps; ++w) o += part[(t * n_warps + w) * LS_COLS + e];
+            for (int u = 0; u < n_units; ++u) o += part[(t * n_units + u) * COLS + e];
             if (MODE == 1) {
                 float nq = 0.0f;
                 for (int w = 0; w < n_warps; ++w) nq += npart[t * n_warps + w];
@@ -212,15 +216,15 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < LS_RW; ++i)
-        if (col_ok && d0 + i < D) st_S[(long)(d0 + i) * E + e0 + lane] = S[i];
+    for (int i = 0; i < RL; ++i)
+        if (col_ok && dl + i < D) st_S[(long)(dl + i) * E + e0 + col] = S[i];
     if (MODE == 1 && blockIdx.x == 0) {
         if (n_mine) st_n[d0 + lane] = n_row;
         if (threadIdx.x == 0) *st_m = *m_s;
     }
 }
 
-static IbDeviceSet scan_smem_set[8];
+static IbDeviceSet scan_smem_set[16];
 
 // proj [rows, ld] act_t holds q and k as [H, D] and v as [H, E] from columns q_col, k_col, v_col on.
 // gates [rows, ld_gates] float: mode 0 the decay's pre-activations [H, D] (gate_bias [H * D], gate_param = tau);
@@ -239,22 +243,31 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
     const long need = (long)H * E * D + (mode == 1 ? (long)H * D + H : 0);
     if (slot_stride < need) return IB_ERR_ARGUMENT;
     const int n_warps = D <= 16 ? 2 : (D + LS_RW - 1) / LS_RW;     // at least two: a thread per (channel, token parity)
-    const dim3 grid((E + LS_COLS - 1) / LS_COLS, H, n_requests);
+    // 16 columns per block where 32 would leave most SMs without one (prompt portions of a few requests).  Measured
+    // at 2,048 tokens of one request with 16 heads of 128 x 128: 0.48 against 0.62 ms with a decay per channel; with
+    // scalar gates 0.96 against 0.72 ms (what a block does once per chunk for all its columns weighs more there), so
+    // that mode keeps 32.
+    const int cols = (mode == 0 && max_rows != 1 && (long)((E + LS_COLS - 1) / LS_COLS) * H * n_requests < 120) ? 16 : LS_COLS;
+    const dim3 grid((E + cols - 1) / cols, H, n_requests);
     const float param = mode == 0 ? 1.0f / gate_param : gate_param;
     const int ch = max_rows == 1 ? 1 : LS_CHUNK;
     auto smem_for = [ch](int warps) {
         return (size_t)(3 * ch * warps * LS_RW + ch * LS_COLS + ch * warps * LS_COLS + ch * warps + 4 * ch + 4) * sizeof(float);
     };
     const size_t smem = smem_for(n_warps);
-#define IB_SCAN_T(MODE, CH, MAXT, SET)                                                                               \
+#define IB_SCAN_C(MODE, CH, MAXT, COLS, SET)                                                                         \
     do {                                                                                                             \
         if (smem > 48 * 1024) { /* the permission is given once per device, for the most that the kernel can ask */  \
-            const int e = ib_allow_dynamic_smem(scan_smem_set[SET], linear_scan_kernel<MODE, CH, MAXT>, smem_for(16)); \
+            const int e = ib_allow_dynamic_smem(scan_smem_set[SET], linear_scan_kernel<MODE, CH, MAXT, COLS>, smem_for(16)); \
             if (e != IB_OK) return e;                                                                                \
         }                                                                                                            \
-        ib_launch(linear_scan_kernel<MODE, CH, MAXT>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld,      \
+        ib_launch(linear_scan_kernel<MODE, CH, MAXT, COLS>, grid, 32 * n_warps, smem, stream, (const act_t*)proj, ld, \
                   q_col, k_col, v_col, gates, ld_gates, gate_bias, param, q_scale, state, slot_stride, q_start,      \
                   slots, out, H, D, E);                                                                              \
+    } while (0)
+#define IB_SCAN_T(MODE, CH, MAXT, SET)                                                                               \
+    do {                                                                                                             \
+        if (cols == 16 && CH > 1) IB_SCAN_C(MODE, LS_CHUNK, MAXT, 16, SET + 8); else IB_SCAN_C(MODE, CH, MAXT, 32, SET); \
     } while (0)
 #define IB_SCAN(MODE, CH, SET)                                                                                       \
     do {                                                                                                             \
@@ -264,6 +277,7 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
     else if (mode == 0) IB_SCAN(0, LS_CHUNK, 1);
     else if (ch == 1) IB_SCAN(1, 1, 2);
     else IB_SCAN(1, LS_CHUNK, 3);
+#undef IB_SCAN_C
 #undef IB_SCAN_T
 #undef IB_SCAN
     return ib_launch_status();
