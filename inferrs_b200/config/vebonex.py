@@ -14,10 +14,13 @@ gated-linear-attention layer's decay (the rows of ``l<i>.mix.a1``).  :meth:`Vebo
 from the weight files' headers; a configuration without weight files (random weights) gives it as ``mixer.a_rank``.
 
 A key that the chosen mixer needs and that is absent is an error: no size stands in code.  Keys that this reader
-does not know are an error too, so that a variant of the design is refused instead of being run as this one.
+does not know inside `norm`, a layer, its mixer or its feed-forward are an error too, so that a variant of the design
+is refused instead of being run as this one; an unknown key at the top (a seed, a name) is named on standard error
+and ignored.
 """
 from __future__ import annotations
 
+import sys
 from dataclasses import dataclass
 from typing import Any, Dict, Optional, Tuple
 
@@ -59,7 +62,11 @@ class VebonexConfig:
                  "layers", "eos_token_id"}
         extra = sorted(k for k in raw.values if k not in known)
         if extra:
-            raise ConfigError(f"{src}: keys {extra} are not part of a Vebonex configuration")
+            # a key beside the model's own (a seed, a name, a storage dtype) changes no arithmetic that this reader
+            # knows of: it is named and left alone.  Unknown keys inside 'norm', a layer, its mixer or its feed-forward
+            # are refused below, since those are where a variant of the design would say what it does differently.
+            print(f"[inferrs_b200] {src}: keys {extra} are not part of a Vebonex configuration and are ignored",
+                  file=sys.stderr)
         missing = [k for k in ("vocab", "width", "max_positions", "norm", "layers") if not raw.has(k)]
         if missing:
             raise ConfigError(f"{src}: Vebonex config lacks the keys {missing}")

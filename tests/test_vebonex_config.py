@@ -52,7 +52,6 @@ def test_the_decay_rank_comes_from_the_tensor_shapes():
     (lambda c: c["layers"][2]["mixer"].update(kv_from=1), "kv_from"),
     (lambda c: c["layers"][2]["mixer"].update(kv_rank=20), "kv_from"),
     (lambda c: c["norm"].update(groups=5), "divisor"),
-    (lambda c: c.update(rope_theta=1e4), "not part of"),
     (lambda c: c["layers"][0].update(mlp={"kind": "routed", "ff": 8}), "mlp"),
 ])
 def test_wrong_configurations_are_refused(edit, message):
@@ -60,6 +59,13 @@ def test_wrong_configurations_are_refused(edit, message):
     edit(cfg)
     with pytest.raises(ConfigError, match=message):
         spec_from_config(cfg)
+
+
+def test_an_unknown_key_at_the_top_is_named_and_ignored(capsys):
+    cfg = copy.deepcopy(CASE_Q)
+    cfg["seed"] = 1234
+    spec, _ = spec_from_config(cfg)
+    assert spec.width == 64 and "seed" in capsys.readouterr().err
 
 
 def test_plain_scans_carry_their_state_across_a_cut():
