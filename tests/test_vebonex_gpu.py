@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = [torch.float32, torch.bfloat16]
 TOL = {torch.float32: 2e-4, torch.bfloat16: 5e-2}
-SEEDS = {"P": 11, "Q": 12, "R": 13}
+SEEDS = {"P": 11, "Q": 12, "R": 13, "S": 14}
 
 
 def assert_close(got, want, dtype):
@@ -58,7 +58,7 @@ def entry(rid, tokens, want=None):
 # whole models
 # ---------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_whole_prompt_and_every_cutting_match_the_plain_statement(name, dtype):
     case, w = CASES[name], make_weights(CASES[name], SEEDS[name])
     toks = random_tokens(75, case["vocab"], seed=3)

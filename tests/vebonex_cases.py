@@ -53,7 +53,18 @@ CASE_R = {
         {"type": "latent_attention", "mixer": _latent(18, 16, 8, 32, 64, 0.25), "mlp": _ff(192)},
     ],
 }
-CASES = {"P": CASE_P, "Q": CASE_Q, "R": CASE_R}
+# sizes that no vector load, tensor-core tile or 16-byte copy takes: a width of 90 in three parts, one head everywhere,
+# inner sizes of 3 and 50
+CASE_S = {
+    "architecture": "Vebonex", "vocab": 77, "width": 90, "max_positions": 300, "streams": 3,
+    "norm": {"eps": 1e-5, "groups": 3},
+    "layers": [
+        {"type": "mlstm", "mixer": {"heads": 1, "dim": 24, "vdim": 10, "gate_cap": 9.0}, "mlp": _ff(50)},
+        {"type": "latent_attention", "mixer": _latent(1, 24, 10, 12, 20, 0.3), "mlp": _ff(50)},
+        {"type": "gla", "mixer": {"heads": 1, "dim": 10, "vdim": 7, "tau": 3.0, "a_rank": 3}, "mlp": None},
+    ],
+}
+CASES = {"P": CASE_P, "Q": CASE_Q, "R": CASE_R, "S": CASE_S}
 
 
 def make_weights(config: dict, seed: int) -> Dict[str, torch.Tensor]:
