@@ -29,6 +29,9 @@ class KVNeed:
     window: Optional[int] = None
     # 2: keys and values each have their pages; 1: one vector per token serves as both (a cache of latents)
     planes: int = 2
+    # size of a value head where it differs from a key head's (None: the same; such a group keeps its values in
+    # a tensor of their own)
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -73,20 +76,31 @@ class CacheStorage:
         self.layouts = [GroupLayout(name=f"group{g}(heads={k.n_kv_heads},dim={k.head_dim},window={k.window})",
                                     window=k.window) for g, k in enumerate(keys)]
         self.n_pages = list(n_pages_per_group) if n_pages_per_group is not None else [n_pages] * len(keys)
+        if any(k.value_dim is not None and k.planes != 2 for k in keys):
+            raise ValueError("values of a size of their own need a cache of two planes")
         self.kv: List[torch.Tensor] = []
+        # values whose heads have another size than the keys': [caches in group, pages, kv_heads, page_size, value_dim]
+        # (the group's tensor in ``kv`` then holds the keys alone)
+        self.values: List[Optional[torch.Tensor]] = []
         for g, k in enumerate(keys):
-            self.kv.append(torch.zeros((len(members[g]), k.planes, self.n_pages[g], k.n_kv_heads, page_size, k.head_dim),
-                                       dtype=dtype, device=device))
+            own_values = k.value_dim is not None and k.value_dim != k.head_dim
+            self.kv.append(torch.zeros((len(members[g]), 1 if own_values else k.planes, self.n_pages[g], k.n_kv_heads,
+                                        page_size, k.head_dim), dtype=dtype, device=device))
+            self.values.append(torch.zeros((len(members[g]), self.n_pages[g], k.n_kv_heads, page_size, k.value_dim),
+                                           dtype=dtype, device=device) if own_values else None)
         # one slot more than there are requests: the requests that only pad a replayed step write their state there
         self.states: Dict[int, torch.Tensor] = {
             cid: torch.zeros((max_requests + 1,) + tuple(need.shape), dtype=need.dtype, device=device)
             for cid, need in state_needs.items()}
 
     def pages(self, cache_id: int) -> Tuple[torch.Tensor, torch.Tensor, int]:
-        """(key pages, value pages, group index) of one cache; pages are [n_pages, kv_heads, page_size, head_dim].
+        """(key pages, value pages, group index) of one cache; pages are [n_pages, kv_heads, page_size, head_dim]
+        (value pages end in the group's ``value_dim`` where it has one).
         A cache of one plane gives the same pages twice."""
         g = self.group_of[cache_id]
         t = self.kv[g][self.index_in_group[cache_id]]
+        if self.values[g] is not None:
+            return t[0], self.values[g][self.index_in_group[cache_id]], g
         return t[0], t[t.shape[0] - 1], g
 
     def state(self, cache_id: int) -> torch.Tensor:
@@ -108,8 +122,10 @@ class CacheStorage:
     def bytes_per_token(self) -> int:
         """Bytes of keys and values that one token adds, over all groups."""
         e = torch.empty((), dtype=self.dtype).element_size()
-        return sum(k.planes * len(self.members[g]) * k.n_kv_heads * k.head_dim * e for g, k in enumerate(self.needs))
+        return sum(len(self.members[g]) * k.n_kv_heads * (k.head_dim * (k.planes - 1) + (k.value_dim or k.head_dim)) * e
+                   for g, k in enumerate(self.needs))
 
     def total_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv) + \
+            sum(t.numel() * t.element_size() for t in self.values if t is not None) + \
             sum(t.numel() * t.element_size() for t in self.states.values())

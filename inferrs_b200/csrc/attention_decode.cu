@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(THREADS, 2) decode_kernel(const __grid_constan
     const int req = P.reqs != nullptr ? P.reqs[place] : place;
     const int G = P.n_heads / P.n_kv_heads;
     const int pos = P.positions[row];
-    const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+    const int lo = ib_first_visible(pos, P.window);
     const int t_first = lo / KEYS, t_last = pos / KEYS + 1;
     const int n_all = t_last - t_first;
     int n_splits = (n_all + P.min_tiles - 1) / P.min_tiles;

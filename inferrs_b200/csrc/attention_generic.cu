@@ -2,7 +2,8 @@
 // (token, query head), 32-bit arithmetic throughout.
 //
 // A token at position `pos` of its request sees the keys lo..pos of that request,
-// lo = 0 or pos - window + 1.  This step's keys are already in the cache when the
+// lo = 0, pos - window + 1, or (window < 0) the first position of pos's chunk of -window positions.  Values may
+// have another size than keys.  This step's keys are already in the cache when the
 // kernel runs, so a prompt portion and a decoded token are the same case.  Keys are
 // taken 32 at a time in ascending order from a multiple of 32, with an online
 // softmax; the order of every sum depends only on (pos, window), never on what else
@@ -14,12 +15,12 @@
 
 #define ATT_WARPS 4
 
-template <int DPL>  // head-size elements per lane: head_dim <= 32 * DPL
+template <int DPL>  // value elements per lane: v_dim <= 32 * DPL
 __global__ void paged_attention_generic_kernel(
     const act_t* __restrict__ q, const act_t* __restrict__ k_pages, const act_t* __restrict__ v_pages,
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
     const int* __restrict__ row_request, const int* __restrict__ positions, int n_heads, int n_kv_heads,
-    int head_dim, float scale, int window, act_t* __restrict__ out) {
+    int head_dim, int v_dim, float scale, int window, act_t* __restrict__ out) {
     extern __shared__ float smem[];
     ib_grid_dependency_sync();
     const int row = blockIdx.x;
@@ -30,7 +31,7 @@ __global__ void paged_attention_generic_kernel(
     float* qs = smem + warp * d;
     const int pos = positions[row];
     const int req = row_request[row];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = ib_first_visible(pos, window);
     const int kvh = head / (n_heads / n_kv_heads);
     const int* bt = block_table + (long)req * max_pages;
 
@@ -47,12 +48,12 @@ __global__ void paged_attention_generic_kernel(
         const int j = j0 + lane;
         const bool valid = j >= lo && j <= pos;
         float s = -INFINITY;
-        long off = 0;
+        long off = 0;      // the key's place counted in heads' rows; times d its key, times v_dim its value
         if (valid) {
             const int page = bt[j / page_size];
             if (page >= 0 && page < n_pages) {
-                off = (((long)page * n_kv_heads + kvh) * page_size + (j % page_size)) * d;
-                const act_t* kr = k_pages + off;
+                off = ((long)page * n_kv_heads + kvh) * page_size + (j % page_size);
+                const act_t* kr = k_pages + off * d;
                 float dot = 0.0f;
                 for (int e = 0; e < d; ++e) dot = fmaf(qs[e], ib_to_float(kr[e]), dot);
                 s = dot * scale;
@@ -69,43 +70,44 @@ __global__ void paged_attention_generic_kernel(
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const long voff = __shfl_sync(0xffffffffu, off, jj);
             if (pj == 0.0f) continue;  // masked key (uniform over the warp)
-            const act_t* vr = v_pages + voff;
+            const act_t* vr = v_pages + voff * v_dim;
 #pragma unroll
             for (int k = 0; k < DPL; ++k) {
                 const int e = lane + 32 * k;
-                if (e < d) acc[k] = fmaf(pj, ib_to_float(vr[e]), acc[k]);
+                if (e < v_dim) acc[k] = fmaf(pj, ib_to_float(vr[e]), acc[k]);
             }
         }
         m = m_new;
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    act_t* dst = out + ((long)row * n_heads + head) * d;
+    act_t* dst = out + ((long)row * n_heads + head) * v_dim;
 #pragma unroll
     for (int k = 0; k < DPL; ++k) {
         const int e = lane + 32 * k;
-        if (e < d) dst[e] = ib_from_float<act_t>(acc[k] * inv);
+        if (e < v_dim) dst[e] = ib_from_float<act_t>(acc[k] * inv);
     }
 }
 
 IB_EXPORT int ib_paged_attention_generic(const void* q, const void* k_pages, const void* v_pages,
                                          const int* block_table, int max_pages, int page_size, int n_pages,
                                          const int* row_request, const int* positions, int n_rows, int n_heads,
-                                         int n_kv_heads, int head_dim, float scale, int window, void* out,
+                                         int n_kv_heads, int head_dim, int v_dim, float scale, int window, void* out,
                                          cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim <= 0 || page_size <= 0 || max_pages <= 0)
         return IB_ERR_ARGUMENT;
-    if (head_dim > 512) return IB_ERR_UNSUPPORTED;
+    if (v_dim <= 0) return IB_ERR_ARGUMENT;
+    if (head_dim > 512 || v_dim > 512) return IB_ERR_UNSUPPORTED;
     const dim3 grid(n_rows, (n_heads + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * head_dim * sizeof(float);
 #define IB_LAUNCH_ATT(DPL)                                                                                      \
     ib_launch(paged_attention_generic_kernel<DPL>, grid, 32 * ATT_WARPS, smem, stream,                          \
         (const act_t*)q, (const act_t*)k_pages, (const act_t*)v_pages, block_table, max_pages, page_size,       \
-        n_pages, row_request, positions, n_heads, n_kv_heads, head_dim, scale, window, (act_t*)out)
-    if (head_dim <= 32) IB_LAUNCH_ATT(1);
-    else if (head_dim <= 64) IB_LAUNCH_ATT(2);
-    else if (head_dim <= 128) IB_LAUNCH_ATT(4);
-    else if (head_dim <= 256) IB_LAUNCH_ATT(8);
+        n_pages, row_request, positions, n_heads, n_kv_heads, head_dim, v_dim, scale, window, (act_t*)out)
+    if (v_dim <= 32) IB_LAUNCH_ATT(1);
+    else if (v_dim <= 64) IB_LAUNCH_ATT(2);
+    else if (v_dim <= 128) IB_LAUNCH_ATT(4);
+    else if (v_dim <= 256) IB_LAUNCH_ATT(8);
     else IB_LAUNCH_ATT(16);
 #undef IB_LAUNCH_ATT
     return ib_launch_status();

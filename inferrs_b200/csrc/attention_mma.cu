@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
     if (n_tok > tpt) n_tok = tpt;
     const int p0 = P.positions[row0];
     const int pmax = p0 + n_tok - 1;
-    const int lo_min = (P.window > 0 && p0 - P.window + 1 > 0) ? p0 - P.window + 1 : 0;
+    const int lo_min = ib_first_visible(p0, P.window);
     const int t_first = lo_min / AM_KEYS, t_last = pmax / AM_KEYS + 1;
     int t_begin = t_first, t_end = t_last;
     if (DECODE && P.n_splits > 1) {
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
         const int ti = r / G;
         if (ti < n_tok) {
             pos_r[h] = p0 + ti;
-            lo_r[h] = (P.window > 0 && pos_r[h] - P.window + 1 > 0) ? pos_r[h] - P.window + 1 : 0;
+            lo_r[h] = ib_first_visible(pos_r[h], P.window);
         } else {
             pos_r[h] = -1;  // no key satisfies lo <= j <= pos
             lo_r[h] = 0;

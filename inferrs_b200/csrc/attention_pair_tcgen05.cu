@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_pair_kernel(const __grid
     const int p0 = P.positions[row0];
     // key tiles that each query tile walks: from the first one that its first token's window reaches (the same
     // for both: the earlier tile's) to the one that holds its last token
-    const int lo_min = (P.window > 0 && p0 - P.window + 1 > 0) ? p0 - P.window + 1 : 0;
+    const int lo_min = ib_first_visible(p0, P.window);
     const int t_begin = lo_min / KEYS;
     const int n_tok_t[2] = {n_tok < tpt ? n_tok : tpt, n_tok > tpt ? n_tok - tpt : 0};
     int n_tiles_t[2];
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_pair_kernel(const __grid
         const int ti = r / G, g = r - ti * G;
         const bool row_valid = ti < n_tok_t[t];
         const int pos = row_valid ? p0 + t * tpt + ti : -1;
-        const int lo = (row_valid && P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+        const int lo = row_valid ? ib_first_visible(pos, P.window) : 0;
         const unsigned lane_addr = (unsigned)((warp & 3) * 32) << 16;
         const unsigned s_addr = tmem + lane_addr + t * 128;
         const unsigned o_addr = tmem + lane_addr + 256 + t * 128;

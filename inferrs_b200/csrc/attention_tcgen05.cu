@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
     if (n_tok > tpt) n_tok = tpt;
     const int p0 = P.positions[row0];
     const int pmax = p0 + n_tok - 1;
-    const int lo_min = (P.window > 0 && p0 - P.window + 1 > 0) ? p0 - P.window + 1 : 0;
+    const int lo_min = ib_first_visible(p0, P.window);
     const int t_begin = lo_min / KEYS, t_end = pmax / KEYS + 1;   // key tiles
     const int n_tiles = t_end - t_begin;
 
@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
         const int ti = r / G, g = r - ti * G;
         const bool row_valid = ti < n_tok;
         const int pos = row_valid ? p0 + ti : -1;
-        const int lo = (row_valid && P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+        const int lo = row_valid ? ib_first_visible(pos, P.window) : 0;
         float o[64];
 #pragma unroll
         for (int e = 0; e < 64; ++e) o[e] = 0.0f;

@@ -39,6 +39,15 @@ template <> __device__ __forceinline__ __nv_bfloat16 ib_from_float<__nv_bfloat16
     return __float2bfloat16_rn(v);
 }
 
+// The first key that a token at position `pos` sees.  span > 0: a sliding window of that many keys
+// (pos - span + 1, not below 0); span < 0: chunks of -span positions counted from position 0 of the sequence (the
+// first position of pos's own chunk); span == 0: every key from 0 on.
+__device__ __forceinline__ int ib_first_visible(int pos, int span) {
+    if (span > 0) return pos - span + 1 > 0 ? pos - span + 1 : 0;
+    if (span < 0) return pos >= 0 ? (pos / (-span)) * (-span) : 0;
+    return 0;
+}
+
 __device__ __forceinline__ float ib_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -44,10 +44,13 @@ __device__ __forceinline__ bool ib_last_row_of_request(const int* __restrict__ r
     return row + 1 >= n_rows || row_request[row + 1] != row_request[row];
 }
 
+// norm_flags: bit 0 the queries are normed, bit 1 the keys, bit 2 the norm comes after the rotation instead of
+// before it.  A normed kind without a weight is divided by its root mean square and nothing else.  Values are
+// heads of v_dim numbers (their pages [n_pages, n_kv_heads, page_size, v_dim]).
 template <typename WT>
 __global__ void qk_norm_rope_store_kernel(
-    const act_t* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int head_dim, int store_kv,
-    const WT* __restrict__ q_weight, const WT* __restrict__ k_weight, float eps,
+    const act_t* __restrict__ qkv, int row_stride, int n_heads, int n_kv_heads, int head_dim, int v_dim, int store_kv,
+    const WT* __restrict__ q_weight, const WT* __restrict__ k_weight, int norm_flags, float eps,
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_dim, int interleaved, int table_rows,
     const int* __restrict__ positions, const int* __restrict__ row_request,
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
@@ -58,26 +61,40 @@ __global__ void qk_norm_rope_store_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = head_dim;
     const int half = rot_dim / 2;
-    float* sh = smem + warp * d;
+    float* sh = smem + warp * 2 * d;      // the head as it came, and turned
+    float* turned = sh + d;
     const int pos = positions[row];
     const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
     // a position outside the rotation tables: the row is left out and the fault is recorded
     if (pos < 0 || (rot_dim > 0 && pos >= table_rows)) { ib_note_row_fault(row); return; }
 
     // Where this row's key and value go: page and place within the page.
-    long kv_base = -1;  // element offset of (page, kv head 0, slot, 0)
+    long kv_place = -1;  // (page, kv head 0, slot) counted in heads' rows
     if (store_kv) {
         const int req = row_request[row];
         const int page = pos / page_size < max_pages ? block_table[(long)req * max_pages + pos / page_size] : -1;
         if (page >= 0 && page < n_pages)
-            kv_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * d;
+            kv_place = (long)page * n_kv_heads * page_size + (pos % page_size);
     }
-    const bool clear_tail = kv_base >= 0 && ib_last_row_of_request(row_request, row, gridDim.x);
+    const bool clear_tail = kv_place >= 0 && ib_last_row_of_request(row_request, row, gridDim.x);
+    const bool norm_after = (norm_flags & 4) != 0;
 
     // one warp per head: blockIdx.y picks the group of QRS_WARPS heads
     for (int head = blockIdx.y * QRS_WARPS + warp; head < heads_total; head += heads_total) {
-        const act_t* src = qkv + (long)row * row_stride + (long)head * d;
         const int kind = head < n_heads ? 0 : (head < n_heads + n_kv_heads ? 1 : 2);  // 0 q, 1 k, 2 v
+        if (kind == 2) {
+            if (kv_place < 0) continue;
+            const int kvh = head - n_heads - n_kv_heads;
+            const act_t* src = qkv + (long)row * row_stride + (long)(n_heads + n_kv_heads) * d + (long)kvh * v_dim;
+            act_t* dst = v_pages + (kv_place + (long)kvh * page_size) * v_dim;
+            for (int j = lane; j < v_dim; j += 32) dst[j] = src[j];
+            if (clear_tail) {
+                const int behind = (page_size - 1 - pos % page_size) * v_dim;
+                for (int j = lane; j < behind; j += 32) dst[v_dim + j] = ib_from_float<act_t>(0.0f);
+            }
+            continue;
+        }
+        const act_t* src = qkv + (long)row * row_stride + (long)head * d;
         float ss = 0.0f;
         for (int j = lane; j < d; j += 32) {
             const float v = ib_to_float(src[j]);
@@ -88,36 +105,35 @@ __global__ void qk_norm_rope_store_kernel(
         if (kind == 0) {
             dst = q_out + ((long)row * n_heads + head) * d;
         } else {
-            if (kv_base < 0) { __syncwarp(); continue; }
-            const int kvh = head - n_heads - (kind == 2 ? n_kv_heads : 0);
-            dst = (kind == 1 ? k_pages : v_pages) + kv_base + (long)kvh * page_size * d;
-        }
-        if (kind == 2) {
-            for (int j = lane; j < d; j += 32) dst[j] = ib_from_float<act_t>(sh[j]);
-            if (clear_tail) {
-                const int behind = (page_size - 1 - pos % page_size) * d;
-                for (int j = lane; j < behind; j += 32) dst[d + j] = ib_from_float<act_t>(0.0f);
-            }
-            __syncwarp();
-            continue;
+            if (kv_place < 0) { __syncwarp(); continue; }
+            dst = k_pages + (kv_place + (long)(head - n_heads) * page_size) * d;
         }
         const WT* w = kind == 0 ? q_weight : k_weight;
-        if (w != nullptr) {
+        const bool normed = (norm_flags & (kind == 0 ? 1 : 2)) != 0;
+        if (normed && !norm_after) {
             ss = ib_warp_sum(ss);
             const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-            for (int j = lane; j < d; j += 32) sh[j] = sh[j] * inv * ib_to_float(w[j]);
+            for (int j = lane; j < d; j += 32) sh[j] = sh[j] * inv * (w ? ib_to_float(w[j]) : 1.0f);
         }
         __syncwarp();
         const float* c = cos_table + (long)pos * half;
         const float* s = sin_table + (long)pos * half;
         // element i of the first half turns with element i + rot_dim / 2, or (interleaved) element 2i with 2i + 1
+        float ss2 = 0.0f;
         for (int j = lane; j < d; j += 32) {
             float o;
             if (j >= rot_dim) o = sh[j];
             else if (interleaved) o = (j & 1) ? sh[j - 1] * s[j >> 1] + sh[j] * c[j >> 1] : sh[j] * c[j >> 1] - sh[j + 1] * s[j >> 1];
             else if (j < half) o = sh[j] * c[j] - sh[j + half] * s[j];
             else o = sh[j - half] * s[j - half] + sh[j] * c[j - half];
-            dst[j] = ib_from_float<act_t>(o);
+            if (normed && norm_after) { ss2 += o * o; turned[j] = o; }     // read again by the lane that wrote it
+            else dst[j] = ib_from_float<act_t>(o);
+        }
+        if (normed && norm_after) {
+            ss2 = ib_warp_sum(ss2);
+            const float inv = 1.0f / sqrtf(ss2 / (float)d + eps);
+            for (int j = lane; j < d; j += 32)
+                dst[j] = ib_from_float<act_t>(turned[j] * inv * (w ? ib_to_float(w[j]) : 1.0f));
         }
         __syncwarp();  // sh is overwritten by this warp's next head
     }
@@ -340,8 +356,8 @@ __global__ void qk_norm_rope_store_d128_wide_kernel(
 #endif
 
 IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows, int n_heads, int n_kv_heads,
-                                    int head_dim, int store_kv, const void* q_weight, const void* k_weight,
-                                    int weight_is_f32, float eps, const float* cos_table, const float* sin_table,
+                                    int head_dim, int v_dim, int store_kv, const void* q_weight, const void* k_weight,
+                                    int weight_is_f32, int norm_flags, float eps, const float* cos_table, const float* sin_table,
                                     int rot_dim, int interleaved, int table_rows, const int* positions, const int* row_request,
                                     const int* block_table, int max_pages, int page_size, int n_pages,
                                     void* k_pages, void* v_pages, void* q_out, cudaStream_t stream) {
@@ -350,11 +366,15 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
         return IB_ERR_ARGUMENT;
     if (store_kv && (n_kv_heads <= 0 || page_size <= 0 || max_pages <= 0)) return IB_ERR_ARGUMENT;
     if (rot_dim > 0 && (cos_table == nullptr || sin_table == nullptr || table_rows <= 0)) return IB_ERR_ARGUMENT;
-    const size_t smem = (size_t)QRS_WARPS * head_dim * sizeof(float);
+    if (v_dim <= 0 || v_dim > 1024) return IB_ERR_ARGUMENT;
+    const size_t smem = (size_t)QRS_WARPS * 2 * head_dim * sizeof(float);
+    const bool plain_norms = v_dim == head_dim && (norm_flags & 4) == 0 &&
+                             ((norm_flags & 1) != 0) == (q_weight != nullptr) &&
+                             (!store_kv || ((norm_flags & 2) != 0) == (k_weight != nullptr));
     const int heads_total = n_heads + (store_kv ? 2 * n_kv_heads : 0);
     const dim3 grid(n_rows, (heads_total + QRS_WARPS - 1) / QRS_WARPS);
 #if IB_ACT_BF16
-    if (head_dim == 128 && rot_dim == 128 && !interleaved && (row_stride % 4) == 0 && ((uintptr_t)qkv % 8) == 0 &&
+    if (plain_norms && head_dim == 128 && rot_dim == 128 && !interleaved && (row_stride % 4) == 0 && ((uintptr_t)qkv % 8) == 0 &&
         ((uintptr_t)cos_table % 16) == 0 && ((uintptr_t)sin_table % 16) == 0) {
 #define IB_LAUNCH_D128(WT, HPW)                                                                                    \
     ib_launch(qk_norm_rope_store_d128_kernel<WT, HPW>, dim3(n_rows, (heads_total + QRS_WARPS * HPW - 1) / (QRS_WARPS * HPW)), \
@@ -388,13 +408,13 @@ IB_EXPORT int ib_qk_norm_rope_store(const void* qkv, int row_stride, int n_rows,
 #endif
     if (weight_is_f32)
         ib_launch(qk_norm_rope_store_kernel<float>, grid, 32 * QRS_WARPS, smem, stream,
-            (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const float*)q_weight,
-            (const float*)k_weight, eps, cos_table, sin_table, rot_dim, interleaved, table_rows, positions, row_request, block_table,
+            (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, v_dim, store_kv, (const float*)q_weight,
+            (const float*)k_weight, norm_flags, eps, cos_table, sin_table, rot_dim, interleaved, table_rows, positions, row_request, block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
     else
         ib_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, 32 * QRS_WARPS, smem, stream,
-            (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, store_kv, (const __nv_bfloat16*)q_weight,
-            (const __nv_bfloat16*)k_weight, eps, cos_table, sin_table, rot_dim, interleaved, table_rows, positions, row_request,
+            (const act_t*)qkv, row_stride, n_heads, n_kv_heads, head_dim, v_dim, store_kv, (const __nv_bfloat16*)q_weight,
+            (const __nv_bfloat16*)k_weight, norm_flags, eps, cos_table, sin_table, rot_dim, interleaved, table_rows, positions, row_request,
             block_table,
             max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);
     return ib_launch_status();

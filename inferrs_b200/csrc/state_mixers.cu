@@ -1,0 +1,368 @@
+// The small kernels around blocks that norm after the sum and around mixers with a scalar decay per head
+// (a fixed-decay linear attention, a state-space mixer with a short convolution), and a feed-forward of routed
+// experts.  Every sum, norm, gate, decay and angle is float in both builds; act_t is only what the projections
+// hand in and what the next projection reads.
+//
+//   norm after the sum      x <- norm(alpha x + delta) * w, the stream itself normalised, with a copy as act_t
+//   heads to float          slices of a projection's rows as float, rotated by position and scaled where asked
+//   convolution and gates   silu(causal convolution + bias) per channel over a request's rows and the inputs that
+//                           its state keeps, and per head dt = softplus(p + b), keep = exp(-exp(A) dt), take = dt
+//   convolution state       the last taps - 1 inputs of every request, after the step
+//   gate, then norm         (y * silu(z)) divided by the root mean square of each of `groups` parts, times w
+//   clamped gate            min(g, c) * sigmoid(s min(g, c)) * (clamp(u, -c, c) + 1)
+//   router                  top-k of logits + bias, softmax over the chosen, as a dense row of weights
+//   routed gate             silu(g) * u * weight of the column's expert
+#include "common.cuh"
+
+__device__ __forceinline__ float sm_silu(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sm_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sm_softplus(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+// ---------------------------------------------------------------------------
+// residual[r, :] <- (alpha * residual[r, :] + delta[r, :]) / rms * weight   (in place, float)
+// copy[r, :] = the same as act_t (what the next sub-layer reads; may be absent).  delta may be absent.
+// ---------------------------------------------------------------------------
+__global__ void scaled_add_norm_kernel(float* __restrict__ residual, const act_t* __restrict__ delta, float alpha,
+                                       const float* __restrict__ weight, float eps, act_t* __restrict__ copy,
+                                       int width) {
+    __shared__ float red[32];
+    ib_grid_dependency_sync();
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float v = alpha * residual[base + j];
+        if (delta) v += ib_to_float(delta[base + j]);
+        residual[base + j] = v;          // read again below by the thread that wrote it
+        ss += v * v;
+    }
+    ss = ib_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = residual[base + j] * inv * weight[j];
+        residual[base + j] = v;
+        if (copy) copy[base + j] = ib_from_float<act_t>(v);
+    }
+}
+
+IB_EXPORT int ib_scaled_add_norm(float* residual, const void* delta, float alpha, const float* weight, float eps,
+                                 void* copy, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (width <= 0 || residual == nullptr || weight == nullptr) return IB_ERR_ARGUMENT;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    ib_launch(scaled_add_norm_kernel, n_rows, threads, 0, stream, residual, (const act_t*)delta, alpha, weight, eps,
+              (act_t*)copy, width);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Up to three slices of a projection's rows as float: slice s is n_heads[s] heads of dim[s] numbers from column
+// src_col[s] on, written from column dst_col[s] of the float rows; where rotate[s] is set the first rot_dim of
+// each head turn by the row's position (element i with i + rot_dim / 2; tables [positions, rot_dim / 2]); every
+// number is multiplied by scale[s].
+// ---------------------------------------------------------------------------
+struct HeadSlices {
+    int n, src_col[3], dst_col[3], n_heads[3], dim[3], rotate[3];
+    float scale[3];
+};
+
+__global__ void heads_to_float_kernel(const act_t* __restrict__ src, long ld, HeadSlices P, float* __restrict__ dst,
+                                      long dst_ld, const float* __restrict__ cos_table,
+                                      const float* __restrict__ sin_table, int rot_dim, int table_rows,
+                                      const int* __restrict__ positions) {
+    ib_grid_dependency_sync();
+    const int row = blockIdx.x;
+    const act_t* in = src + (long)row * ld;
+    float* out = dst + (long)row * dst_ld;
+    const int half = rot_dim / 2;
+    int pos = positions ? positions[row] : 0;
+    if (pos < 0) pos = 0;
+    if (pos >= table_rows) pos = table_rows - 1;     // the host sizes the tables for every position of the model
+    for (int s = 0; s < P.n; ++s) {
+        const int d = P.dim[s], total = P.n_heads[s] * d;
+        const float scale = P.scale[s];
+        for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+            const int j = idx % d;
+            const act_t* h = in + P.src_col[s] + (idx - j);
+            float v = ib_to_float(h[j]);
+            if (P.rotate[s] && j < rot_dim) {
+                const int i = j < half ? j : j - half;
+                const float c = cos_table[(long)pos * half + i], sn = sin_table[(long)pos * half + i];
+                v = j < half ? v * c - ib_to_float(h[j + half]) * sn : v * c + ib_to_float(h[j - half]) * sn;
+            }
+            out[P.dst_col[s] + idx] = v * scale;
+        }
+    }
+}
+
+IB_EXPORT int ib_heads_to_float(const void* src, long ld, int n_slices, const int* src_col, const int* dst_col,
+                                const int* n_heads, const int* dim, const int* rotate, const float* scale, float* dst,
+                                long dst_ld, const float* cos_table, const float* sin_table, int rot_dim, int table_rows,
+                                const int* positions, int n_rows, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (n_slices < 1 || n_slices > 3 || src == nullptr || dst == nullptr || rot_dim < 0 || (rot_dim & 1))
+        return IB_ERR_ARGUMENT;
+    HeadSlices P;
+    P.n = n_slices;
+    int widest = 0;
+    for (int s = 0; s < n_slices; ++s) {
+        P.src_col[s] = src_col[s]; P.dst_col[s] = dst_col[s]; P.n_heads[s] = n_heads[s]; P.dim[s] = dim[s];
+        P.rotate[s] = rotate[s]; P.scale[s] = scale[s];
+        if (n_heads[s] <= 0 || dim[s] <= 0 || (rotate[s] && rot_dim > dim[s])) return IB_ERR_ARGUMENT;
+        if (rotate[s] && rot_dim > 0 && (cos_table == nullptr || sin_table == nullptr || positions == nullptr ||
+                                        table_rows <= 0))
+            return IB_ERR_ARGUMENT;
+        if (n_heads[s] * dim[s] > widest) widest = n_heads[s] * dim[s];
+    }
+    const int threads = widest >= 1024 ? 256 : 128;
+    ib_launch(heads_to_float_kernel, n_rows, threads, 0, stream, (const act_t*)src, ld, P, dst, dst_ld, cos_table,
+              sin_table, rot_dim, table_rows, positions);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Channel c < C of row r:  out[r, c] = silu(bias[c] + sum_j w[c, j] * input(r - (taps - 1 - j), c)),
+// where input(t, c) is the projection's column conv_col + c of row t if t is a row of the same request in this
+// step, and else what the request's state keeps: its last taps - 1 inputs, oldest first, [taps - 1, C] floats at
+// conv_state_off of its slot (zeros for a new request: nothing stands before the start).
+// Head h of row r (threads C .. C + H - 1):  dt = softplus(proj[r, dt_col + h] + dt_bias[h]),
+// gates[r, h] = exp(-exp(a_log[h]) dt)  (what the state keeps),  gates[r, H + h] = dt  (what the input is taken by).
+// ---------------------------------------------------------------------------
+__global__ void conv_silu_gates_kernel(const act_t* __restrict__ proj, long ld, int conv_col, int C, int taps,
+                                       const float* __restrict__ w, const float* __restrict__ bias,
+                                       const float* __restrict__ state, long slot_stride, long conv_state_off,
+                                       const int* __restrict__ q_start, const int* __restrict__ slots,
+                                       const int* __restrict__ row_request, float* __restrict__ out, int dt_col, int H,
+                                       const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                       float* __restrict__ gates) {
+    ib_grid_dependency_sync();
+    const int row = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C + H) return;
+    const act_t* in = proj + (long)row * ld;
+    if (c >= C) {
+        const int h = c - C;
+        const float dt = sm_softplus(ib_to_float(in[dt_col + h]) + dt_bias[h]);
+        gates[(long)row * 2 * H + h] = expf(-expf(a_log[h]) * dt);
+        gates[(long)row * 2 * H + H + h] = dt;
+        return;
+    }
+    const int req = row_request[row];
+    const int row0 = q_start[req];
+    const float* kept = state + (long)slots[req] * slot_stride + conv_state_off;
+    float acc = bias[c];
+    for (int j = 0; j < taps; ++j) {
+        const int t = row - (taps - 1 - j);
+        float v;
+        if (t >= row0) v = ib_to_float(proj[(long)t * ld + conv_col + c]);
+        else v = kept[(long)(taps - 1 - (row0 - t)) * C + c];
+        acc = fmaf(w[(long)c * taps + j], v, acc);
+    }
+    out[(long)row * C + c] = sm_silu(acc);
+}
+
+IB_EXPORT int ib_conv_silu_gates(const void* proj, long ld, int conv_col, int C, int taps, const float* w,
+                                 const float* bias, const float* state, long slot_stride, long conv_state_off,
+                                 const int* q_start, const int* slots, const int* row_request, float* out, int dt_col,
+                                 int H, const float* dt_bias, const float* a_log, float* gates, int n_rows,
+                                 cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (C <= 0 || taps <= 0 || H <= 0 || proj == nullptr || w == nullptr || bias == nullptr || state == nullptr ||
+        out == nullptr || gates == nullptr || dt_bias == nullptr || a_log == nullptr ||
+        slot_stride < conv_state_off + (long)(taps - 1) * C)
+        return IB_ERR_ARGUMENT;
+    if (n_rows > 65535) return IB_ERR_UNSUPPORTED;
+    const int threads = 128;
+    ib_launch(conv_silu_gates_kernel, dim3((C + H + threads - 1) / threads, n_rows), threads, 0, stream,
+              (const act_t*)proj, ld, conv_col, C, taps, w, bias, state, slot_stride, conv_state_off, q_start, slots,
+              row_request, out, dt_col, H, dt_bias, a_log, gates);
+    return ib_launch_status();
+}
+
+// After the step: every request's state keeps its last taps - 1 inputs, oldest first.  A request that brought
+// fewer rows than that keeps the youngest of what it held before them.  One thread per (request, channel) writes
+// place k after it has read everything it needs from places above k.
+__global__ void conv_state_shift_kernel(const act_t* __restrict__ proj, long ld, int conv_col, int C, int taps,
+                                        float* __restrict__ state, long slot_stride, long conv_state_off,
+                                        const int* __restrict__ q_start, const int* __restrict__ slots) {
+    ib_grid_dependency_sync();
+    const int req = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int row0 = q_start[req], n = q_start[req + 1] - row0;
+    if (n <= 0) return;
+    float* kept = state + (long)slots[req] * slot_stride + conv_state_off;
+    for (int k = 0; k < taps - 1; ++k) {
+        const int idx = n - (taps - 1) + k;      // which of the step's rows belongs at place k
+        kept[(long)k * C + c] = idx >= 0 ? ib_to_float(proj[(long)(row0 + idx) * ld + conv_col + c])
+                                         : kept[(long)(k + n) * C + c];
+    }
+}
+
+IB_EXPORT int ib_conv_state_shift(const void* proj, long ld, int conv_col, int C, int taps, float* state,
+                                  long slot_stride, long conv_state_off, const int* q_start, const int* slots,
+                                  int n_requests, cudaStream_t stream) {
+    if (n_requests <= 0 || taps <= 1) return IB_OK;
+    if (C <= 0 || proj == nullptr || state == nullptr || n_requests > 65535) return IB_ERR_ARGUMENT;
+    const int threads = 128;
+    ib_launch(conv_state_shift_kernel, dim3((C + threads - 1) / threads, n_requests), threads, 0, stream,
+              (const act_t*)proj, ld, conv_col, C, taps, state, slot_stride, conv_state_off, q_start, slots);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// out[r, :] = norm_in_groups(y[r, :] * silu(z[r, :])) * weight: the gate comes before the norm; each of `groups`
+// equal consecutive parts of the row is divided by its own root mean square.  One warp per part.
+// ---------------------------------------------------------------------------
+__global__ void gate_group_norm_kernel(const float* __restrict__ y, const act_t* __restrict__ z, long z_ld,
+                                       const float* __restrict__ weight, int groups, int part, float eps,
+                                       act_t* __restrict__ out) {
+    ib_grid_dependency_sync();
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const long inner = (long)groups * part;
+    for (int g = warp; g < groups; g += n_warps) {
+        const float* yr = y + (long)row * inner + (long)g * part;
+        const act_t* zr = z + (long)row * z_ld + (long)g * part;
+        float ss = 0.0f;
+        for (int j = lane; j < part; j += 32) {
+            const float v = yr[j] * sm_silu(ib_to_float(zr[j]));
+            ss += v * v;
+        }
+        ss = ib_warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)part + eps);
+        for (int j = lane; j < part; j += 32) {
+            const float v = yr[j] * sm_silu(ib_to_float(zr[j]));
+            out[(long)row * inner + (long)g * part + j] = ib_from_float<act_t>(v * inv * weight[(long)g * part + j]);
+        }
+    }
+}
+
+IB_EXPORT int ib_gate_group_norm(const float* y, const void* z, long z_ld, const float* weight, int groups, int inner,
+                                 float eps, void* out, int n_rows, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (groups <= 0 || inner <= 0 || inner % groups || y == nullptr || z == nullptr || weight == nullptr)
+        return IB_ERR_ARGUMENT;
+    const int warps = groups < 8 ? groups : 8;
+    ib_launch(gate_group_norm_kernel, n_rows, 32 * warps, 0, stream, y, (const act_t*)z, z_ld, weight, groups,
+              inner / groups, eps, (act_t*)out);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// out[r, j] = g' * sigmoid(slope * g') * (u' + 1),  g' = min(gate_up[r, j], limit),
+// u' = clamp(gate_up[r, inner + j], -limit, limit)
+// ---------------------------------------------------------------------------
+__global__ void clamped_gate_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total,
+                                    float limit, float slope) {
+    ib_grid_dependency_sync();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / inner;
+        const int j = (int)(i - r * inner);
+        const float g = fminf(ib_to_float(gate_up[r * 2 * inner + j]), limit);
+        const float u = fminf(fmaxf(ib_to_float(gate_up[r * 2 * inner + inner + j]), -limit), limit);
+        out[i] = ib_from_float<act_t>(g * sm_sigmoid(slope * g) * (u + 1.0f));
+    }
+}
+
+IB_EXPORT int ib_clamped_gate(const void* gate_up, void* out, int n_rows, int inner, float limit, float slope,
+                              cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (inner <= 0 || !(limit > 0.0f)) return IB_ERR_ARGUMENT;
+    const long total = (long)n_rows * inner;
+    long blocks = (total + 255) / 256;
+    if (blocks > 148L * 16) blocks = 148L * 16;
+    ib_launch(clamped_gate_kernel, (int)blocks, 256, 0, stream, (const act_t*)gate_up, (act_t*)out, inner, total, limit,
+              slope);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Router.  logits [rows, ld] float hold n_experts router logits per row (and, with has_shared, one more column:
+// the shared expert's gate).  weights[r, e] = softmax over the `top` largest of logits[r, :] + bias among
+// themselves for those experts, 0 for the others (equal logits: the lower index wins);
+// weights[r, n_experts] = sigmoid(logits[r, n_experts]).  One warp per row.
+// ---------------------------------------------------------------------------
+__global__ void router_topk_kernel(const float* __restrict__ logits, long ld, const float* __restrict__ bias,
+                                   int n_experts, int top, int has_shared, float* __restrict__ weights, int n_rows) {
+    ib_grid_dependency_sync();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const float* z = logits + (long)row * ld;
+    float* w = weights + (long)row * (n_experts + has_shared);
+    // a chosen expert is marked by a weight of -1 until the softmax replaces it
+    for (int e = lane; e < n_experts; e += 32) w[e] = 0.0f;
+    __syncwarp();
+    float first = 0.0f, sum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = z[e] + (bias ? bias[e] : 0.0f);
+            if (w[e] == 0.0f && (v > best || (v == best && e < at))) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at == 0x7fffffff) break;        // fewer experts than `top`, or nothing but NaN
+        if (k == 0) first = best;
+        sum += expf(best - first);
+        if (lane == 0) w[at] = -1.0f;
+        __syncwarp();
+    }
+    for (int e = lane; e < n_experts; e += 32)
+        if (w[e] < 0.0f) w[e] = expf(z[e] + (bias ? bias[e] : 0.0f) - first) / sum;
+    if (has_shared && lane == 0) w[n_experts] = sm_sigmoid(z[n_experts]);
+}
+
+IB_EXPORT int ib_router_topk(const float* logits, long ld, const float* bias, int n_experts, int top, int has_shared,
+                             float* weights, int n_rows, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (n_experts <= 0 || top <= 0 || top > n_experts || logits == nullptr || weights == nullptr ||
+        ld < n_experts + (has_shared ? 1 : 0))
+        return IB_ERR_ARGUMENT;
+    const int warps = 4;
+    ib_launch(router_topk_kernel, (n_rows + warps - 1) / warps, 32 * warps, 0, stream, logits, ld, bias, n_experts, top,
+              has_shared ? 1 : 0, weights, n_rows);
+    return ib_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// out[r, j] = silu(gate_up[r, j]) * gate_up[r, inner + j] * weights[r, e(j)]: the columns of all experts side by
+// side, `ff` columns each for the n_experts routed ones (e(j) = j / ff) and the rest for the shared one
+// (e(j) = n_experts).  A token's columns of experts that it did not choose become zero, so the product with the
+// down matrices of all experts, side by side along its inner dimension, is the weighted sum over the chosen.
+// ---------------------------------------------------------------------------
+__global__ void routed_gate_kernel(const act_t* __restrict__ gate_up, const float* __restrict__ weights, int n_weights,
+                                   int n_experts, int ff, act_t* __restrict__ out, int inner, long total) {
+    ib_grid_dependency_sync();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / inner;
+        const int j = (int)(i - r * inner);
+        int e = j / ff;
+        if (e > n_experts) e = n_experts;
+        const float wt = weights[r * n_weights + e];
+        float v = 0.0f;
+        if (wt != 0.0f) {
+            const float g = ib_to_float(gate_up[r * 2 * inner + j]);
+            v = sm_silu(g) * ib_to_float(gate_up[r * 2 * inner + inner + j]) * wt;
+        }
+        out[i] = ib_from_float<act_t>(v);
+    }
+}
+
+IB_EXPORT int ib_routed_gate(const void* gate_up, const float* weights, int n_weights, int n_experts, int ff, void* out,
+                             int n_rows, int inner, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (inner <= 0 || ff <= 0 || n_experts <= 0 || (long)n_experts * ff > inner || weights == nullptr ||
+        n_weights < n_experts + ((long)n_experts * ff < inner ? 1 : 0))
+        return IB_ERR_ARGUMENT;
+    const long total = (long)n_rows * inner;
+    long blocks = (total + 255) / 256;
+    if (blocks > 148L * 16) blocks = 148L * 16;
+    ib_launch(routed_gate_kernel, (int)blocks, 256, 0, stream, (const act_t*)gate_up, weights, n_weights, n_experts, ff,
+              (act_t*)out, inner, total);
+    return ib_launch_status();
+}

@@ -33,12 +33,16 @@ def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
             _check_category(sub.category)
             if sub.norm is not None:
                 decls += part_class("norm", sub.norm).declare(sub.norm)
-            decls += part_class(sub.category, sub.part).declare(sub.part)
-            if sub.post_norm is not None:
-                decls += part_class("norm", sub.post_norm).declare(sub.post_norm)
+            if sub.part is not None:
+                decls += part_class(sub.category, sub.part).declare(sub.part)
+            for after in (sub.post_norm, getattr(sub, "sum_norm", None)):
+                if after is not None:
+                    decls += part_class("norm", after).declare(after)
         decls += _arrangement_tensors(layer)
     if spec.position_table is not None:
         decls.append(TensorDecl(spec.position_table, (spec.max_positions, spec.width)))
+    if spec.embedding_norm is not None:
+        decls += part_class("norm", spec.embedding_norm).declare(spec.embedding_norm)
     decls += part_class("norm", spec.final_norm).declare(spec.final_norm)
     decls.append(TensorDecl(spec.lm_head, (spec.vocab_size, spec.width), optional=spec.lm_head_optional))
     seen, out = {}, []
@@ -117,7 +121,8 @@ def cache_needs(spec: ModelSpec):
 def _layer_tensor_names(layer) -> List[str]:
     names = []
     for sub in layer.sublayers:
-        for kind, d in (("norm", sub.norm), (sub.category, sub.part), ("norm", sub.post_norm)):
+        for kind, d in (("norm", sub.norm), (sub.category, sub.part), ("norm", sub.post_norm),
+                        ("norm", getattr(sub, "sum_norm", None))):
             if d is not None:
                 names += [t.name for t in part_class(kind, d).declare(d)]
     names += [t.name for t in _arrangement_tensors(layer)]
@@ -151,8 +156,11 @@ class Model:
                     else NoNorm(None, weights, rt)
                 post = part_class("norm", sub.post_norm)(sub.post_norm, weights, rt) \
                     if sub.post_norm is not None else None
-                built.append(BuiltSubLayer(sub.category, part_class(sub.category, sub.part)(sub.part, weights, rt),
-                                           norm, post))
+                sum_norm = part_class("norm", sub.sum_norm)(sub.sum_norm, weights, rt) \
+                    if getattr(sub, "sum_norm", None) is not None else None
+                # a sub-layer without a part (an arrangement may allow it) is its norms alone
+                part = part_class(sub.category, sub.part)(sub.part, weights, rt) if sub.part is not None else None
+                built.append(BuiltSubLayer(sub.category, part, norm, post, sum_norm))
             arrangement = part_class("arrangement", _Arrangement(layer.arrangement))
             if getattr(arrangement, "needs_weights", False):
                 self.blocks.append(arrangement(layer, built, weights, rt))
@@ -163,6 +171,12 @@ class Model:
                     if last_use[name] == i and name not in (spec.embedding, spec.lm_head):
                         weights.pop(name, None)
         self._takes_after = ["after" in inspect.signature(b.forward).parameters for b in self.blocks]
+        self.embedding_norm = None
+        if spec.embedding_norm is not None:
+            if spec.streams is not None or getattr(spec.embedding_norm, "groups", 1) != 1:
+                raise ModelError("a norm on the embedding is a plain RMS norm on a residual of one stream")
+            self.embedding_norm = (weights[spec.embedding_norm.weight].to(torch.float32).contiguous(),
+                                   float(spec.embedding_norm.eps))
         self.final_norm = part_class("norm", spec.final_norm)(spec.final_norm, weights, rt)
         head = weights.get(spec.lm_head)
         if head is None:
@@ -187,6 +201,9 @@ class Model:
                                       self.rt.dtype, scale)
             if self.spec.streams is None:
                 residual = residual.view(n, self.spec.width)
+        if self.embedding_norm is not None:
+            kernels.scaled_add_norm(residual, None, 1.0, self.embedding_norm[0], self.embedding_norm[1], None,
+                                    self.rt.dtype)
         pending = None
         schedule = self.spec.schedule
         for k, entry in enumerate(schedule):

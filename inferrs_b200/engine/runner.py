@@ -73,7 +73,8 @@ class ModelRunner:
         gc.collect()
         torch.cuda.empty_cache()        # what the loader and the fusing of tensors have given back
         elem = torch.empty((), dtype=self.rt.dtype).element_size()
-        per_page = sum(n.planes * n.n_kv_heads * n.head_dim * page_size * elem for n in kv_needs.values())
+        per_page = sum(n.n_kv_heads * (n.head_dim * (n.planes - 1) + (getattr(n, 'value_dim', None) or n.head_dim))
+                       * page_size * elem for n in kv_needs.values())
         free, _total = torch.cuda.mem_get_info(self.rt.device)
         pages = int(free * fraction) // max(per_page, 1)
         # no request can use more than max_context tokens: more pages than that per slot are never touched

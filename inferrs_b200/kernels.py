@@ -33,11 +33,12 @@ _SIGNATURES = {
     "ib_add_rms_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "ib_silu_gate": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "ib_act_to_float": [c_void_p, c_void_p, c_long, c_void_p],
-    "ib_qk_norm_rope_store": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
+    "ib_qk_norm_rope_store": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                              c_float,
                               c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p],
     "ib_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
-                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "ib_gemm_tn_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
                         c_long, c_void_p],
     "ib_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -79,6 +80,19 @@ _SIGNATURES = {
                             c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "ib_gemm_tn_simt_batched": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
                                 c_long, c_int, c_long, c_long, c_long, c_void_p],
+    "ib_scaled_add_norm": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p],
+    "ib_heads_to_float": [c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_long, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
+    "ib_conv_silu_gates": [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_long, c_long, c_void_p,
+                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "ib_conv_state_shift": [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_long, c_long, c_void_p, c_void_p, c_int,
+                            c_void_p],
+    "ib_gate_group_norm": [c_void_p, c_void_p, c_long, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "ib_clamped_gate": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p],
+    "ib_router_topk": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "ib_routed_gate": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+    "ib_decay_scan": [c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p,
+                      c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ib_sample": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_int, c_void_p, c_void_p],
 }
@@ -504,12 +518,17 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                        cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dim: int,
                        positions: torch.Tensor, row_request: torch.Tensor, block_table: Optional[torch.Tensor],
                        k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], q_out: torch.Tensor,
-                       interleaved: bool = False):
+                       interleaved: bool = False, norm_q: Optional[bool] = None, norm_k: Optional[bool] = None,
+                       norm_after_rotation: bool = False):
     """Per-head norm of q and k, rotation by position, q to ``q_out``, k and v into their pages.  Element ``i`` of
     a head's first ``rot_dim / 2`` turns with element ``i + rot_dim / 2``; ``interleaved``: element ``2i`` with ``2i + 1``.
 
-    qkv [N, (n_heads + 2 n_kv_heads) * d] (queries only when ``store_kv`` is False);
-    pages [n_pages, n_kv_heads, page_size, d]; block_table int32 [R, max_pages].
+    ``norm_q`` / ``norm_k`` say whether queries / keys are divided by their root mean square (None: where a weight is
+    given); a normed kind without a weight is divided and nothing else.  ``norm_after_rotation``: the norm comes
+    after the rotation instead of before it.  Values may have another size than keys (the last size of ``v_pages``).
+
+    qkv [N, n_heads * d + n_kv_heads * (d + dv)] (queries only when ``store_kv`` is False);
+    pages [n_pages, n_kv_heads, page_size, d or dv]; block_table int32 [R, max_pages].
     """
     act = q_out.dtype
     _need(qkv, "qkv", (act,), 2)
@@ -517,7 +536,11 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
     _need(positions, "positions", _I, 1)
     _need(row_request, "row_request", _I, 1)
     n = qkv.shape[0]
-    cols = (n_heads + (2 * n_kv_heads if store_kv else 0)) * head_dim
+    v_dim = head_dim
+    if store_kv:
+        _need(v_pages, "v_pages", (act,), 4)
+        v_dim = v_pages.shape[3]
+    cols = n_heads * head_dim + (n_kv_heads * (head_dim + v_dim) if store_kv else 0)
     if qkv.shape[1] != cols or q_out.shape != (n, n_heads, head_dim) or positions.shape[0] != n \
             or row_request.shape[0] != n:
         raise KernelError(f"qk_norm_rope_store: qkv {tuple(qkv.shape)} (want {cols} columns), q_out "
@@ -531,6 +554,11 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
             if wdt is not None and w.dtype != wdt:
                 raise KernelError("q_weight and k_weight must have the same dtype")
             wdt = w.dtype
+    norm_q = q_weight is not None if norm_q is None else bool(norm_q)
+    norm_k = k_weight is not None if norm_k is None else bool(norm_k)
+    if (q_weight is not None and not norm_q) or (k_weight is not None and not norm_k):
+        raise KernelError("qk_norm_rope_store: a norm weight was given for a kind that is not normed")
+    flags = int(norm_q) | (int(norm_k) << 1) | (int(bool(norm_after_rotation)) << 2)
     table_rows = 0
     if rot_dim:
         _need(cos, "cos", (torch.float32,), 2)
@@ -542,14 +570,14 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
     if store_kv:
         _need(block_table, "block_table", _I, 2)
         _need(k_pages, "k_pages", (act,), 4)
-        _need(v_pages, "v_pages", (act,), 4)
         n_pages, nkv, page_size, d = k_pages.shape
-        if (nkv, d) != (n_kv_heads, head_dim) or v_pages.shape != k_pages.shape:
-            raise KernelError(f"cache pages {tuple(k_pages.shape)} do not match {n_kv_heads} heads of {head_dim}")
+        if (nkv, d) != (n_kv_heads, head_dim) or v_pages.shape[:3] != k_pages.shape[:3]:
+            raise KernelError(f"cache pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} do not match "
+                              f"{n_kv_heads} heads of {head_dim}")
         max_pages = block_table.shape[1]
     _check(_core(act).ib_qk_norm_rope_store(
-        _p(qkv), cols, n, n_heads, n_kv_heads, head_dim, int(store_kv), _p(q_weight), _p(k_weight),
-        int(wdt == torch.float32), float(eps), _p(cos) if rot_dim else None, _p(sin) if rot_dim else None, rot_dim,
+        _p(qkv), cols, n, n_heads, n_kv_heads, head_dim, v_dim, int(store_kv), _p(q_weight), _p(k_weight),
+        int(wdt == torch.float32), flags, float(eps), _p(cos) if rot_dim else None, _p(sin) if rot_dim else None, rot_dim,
         int(bool(interleaved)), table_rows, _p(positions), _p(row_request), _p(block_table) if store_kv else None, max_pages, page_size,
         n_pages, _p(k_pages) if store_kv else None, _p(v_pages) if store_kv else None, _p(q_out), _stream()),
         "qk_norm_rope_store")
@@ -564,10 +592,21 @@ def row_fault(act_dtype: torch.dtype, reset: bool = True) -> Optional[int]:
     return None if v == 0 else v - 1
 
 
+def span_argument(window: Optional[int], chunk: Optional[int] = None) -> int:
+    """How the attention kernels are told which keys a token sees: 0 all keys up to its own, n > 0 the last n of
+    them (a sliding window), -n its own chunk of n positions counted from position 0 of the sequence."""
+    if window and chunk:
+        raise KernelError("attention: a sliding window and chunks together have no kernel")
+    if (window is not None and window < 0) or (chunk is not None and chunk < 0):
+        raise KernelError(f"attention: a window or a chunk is a positive number of positions, got {window}, {chunk}")
+    return int(window) if window else (-int(chunk) if chunk else 0)
+
+
 def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                             row_request: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
                             out: torch.Tensor):
-    """out[r, h*d:(h+1)*d] = attention of token r's head h over its request's cached keys lo..pos."""
+    """out[r, h*dv:(h+1)*dv] = attention of token r's head h over its request's cached keys lo..pos.  ``window``:
+    see :func:`span_argument` (a negative number: chunks).  Values may have another size dv than keys."""
     act = out.dtype
     _need(q, "q", (act,), 3)
     _need(k_pages, "k_pages", (act,), 4)
@@ -578,13 +617,15 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     _need(out, "out", _W, 2)
     n, nh, d = q.shape
     n_pages, nkv, page_size, dk = k_pages.shape
-    if dk != d or v_pages.shape != k_pages.shape or out.shape != (n, nh * d) or nh % nkv:
-        raise KernelError(f"paged_attention: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
-    if d > 512:
-        raise KernelError(f"paged_attention: head_dim {d} is larger than 512, the largest the kernel takes")
+    dv = v_pages.shape[3]
+    if dk != d or v_pages.shape[:3] != k_pages.shape[:3] or out.shape != (n, nh * dv) or nh % nkv:
+        raise KernelError(f"paged_attention: q {tuple(q.shape)}, pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)}, "
+                          f"out {tuple(out.shape)}")
+    if d > 512 or dv > 512:
+        raise KernelError(f"paged_attention: head sizes {d}, {dv} are larger than 512, the largest the kernel takes")
     _check(_core(act).ib_paged_attention_generic(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(row_request),
-        _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0, _p(out), _stream()),
+        _p(positions), n, nh, nkv, d, dv, float(scale), int(window) if window else 0, _p(out), _stream()),
         "paged_attention_generic")
 
 
@@ -836,6 +877,211 @@ def gated_linear(x, w_gate_up: torch.Tensor, out: torch.Tensor, act_dtype: torch
     silu_gate(gu, out)
 
 
+def scaled_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], alpha: float, weight: torch.Tensor,
+                    eps: float, copy: Optional[torch.Tensor], act_dtype: torch.dtype):
+    """The norm after the sum, on the stream itself: residual <- (alpha * residual + delta) / rms * weight, float32 in
+    place; ``copy`` (may be None) receives the same rows in the activation dtype.  ``delta`` may be None."""
+    _need(residual, "residual", (torch.float32,), 2)
+    _need(delta, "delta", (act_dtype,), 2, optional=True)
+    _need(weight, "weight", (torch.float32,), 1)
+    _need(copy, "copy", (act_dtype,), 2, optional=True)
+    n, width = residual.shape
+    if weight.shape[0] != width or (delta is not None and delta.shape != residual.shape) \
+            or (copy is not None and copy.shape != residual.shape):
+        raise KernelError(f"scaled_add_norm: residual {tuple(residual.shape)}, weight {tuple(weight.shape)}, delta "
+                          f"{None if delta is None else tuple(delta.shape)}")
+    _check(_core(act_dtype).ib_scaled_add_norm(_p(residual), _p(delta), float(alpha), _p(weight), float(eps), _p(copy),
+                                               n, width, _stream()), "scaled_add_norm")
+
+
+def heads_to_float(src: torch.Tensor, slices, dst: torch.Tensor, cos: Optional[torch.Tensor],
+                   sin: Optional[torch.Tensor], rot_dim: int, positions: Optional[torch.Tensor]):
+    """Up to three slices of a projection's rows as float32.  ``slices``: (first column in ``src``, first column in
+    ``dst``, heads, numbers per head, rotate?, scale) each; a rotated slice has the first ``rot_dim`` numbers of each
+    head turned by the row's position (element i with i + rot_dim / 2; float32 tables [positions, rot_dim / 2]); every
+    number is multiplied by the slice's scale."""
+    act = src.dtype
+    _need(src, "src", _W, 2)
+    _need(dst, "dst", (torch.float32,), 2)
+    n = src.shape[0]
+    if dst.shape[0] != n or not 1 <= len(slices) <= 3:
+        raise KernelError(f"heads_to_float: src {tuple(src.shape)}, dst {tuple(dst.shape)}, {len(slices)} slices")
+    turning = any(sl[4] for sl in slices) and rot_dim > 0
+    table_rows = 0
+    if turning:
+        _need(cos, "cos", (torch.float32,), 2)
+        _need(sin, "sin", (torch.float32,), 2)
+        _need(positions, "positions", _I, 1)
+        if cos.shape[1] != rot_dim // 2 or sin.shape != cos.shape or positions.shape[0] != n:
+            raise KernelError(f"heads_to_float: rotation tables {tuple(cos.shape)} do not match rot_dim {rot_dim}")
+        table_rows = cos.shape[0]
+    for a, b, heads, dim, rot, _scale in slices:
+        if a < 0 or b < 0 or a + heads * dim > src.shape[1] or b + heads * dim > dst.shape[1] or (rot and rot_dim > dim):
+            raise KernelError(f"heads_to_float: slice {(a, b, heads, dim)} does not fit src {tuple(src.shape)}, dst "
+                              f"{tuple(dst.shape)}")
+    k = len(slices)
+    ints = [(c_int * k)(*[int(sl[i]) for sl in slices]) for i in range(5)]
+    scales = (c_float * k)(*[float(sl[5]) for sl in slices])
+    _check(_core(act).ib_heads_to_float(
+        _p(src), src.shape[1], k, ints[0], ints[1], ints[2], ints[3], ints[4], scales, _p(dst), dst.shape[1],
+        _p(cos) if turning else None, _p(sin) if turning else None, int(rot_dim) if turning else 0, table_rows,
+        _p(positions) if turning else None, n, _stream()), "heads_to_float")
+
+
+def conv_silu_gates(proj: torch.Tensor, conv_col: int, conv_w: torch.Tensor, conv_b: torch.Tensor, state: torch.Tensor,
+                    conv_state_off: int, q_start: torch.Tensor, slots: torch.Tensor, row_request: torch.Tensor,
+                    out: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, gates: torch.Tensor):
+    """out[r, c] = silu(b[c] + sum_j w[c, j] * input(r - (taps - 1 - j), c)) for the C channels from column
+    ``conv_col`` of ``proj``; an input before the request's first row of the step comes from its state (the last
+    taps - 1 inputs, oldest first, [taps - 1, C] float32 from ``conv_state_off`` of its slot).  And per head,
+    dt = softplus(proj[r, dt_col + h] + dt_bias[h]): gates[r, h] = exp(-exp(a_log[h]) dt), gates[r, H + h] = dt."""
+    act = proj.dtype
+    _need(proj, "proj", _W, 2)
+    for name, t, nd in (("conv_w", conv_w, 2), ("conv_b", conv_b, 1), ("dt_bias", dt_bias, 1), ("a_log", a_log, 1),
+                        ("out", out, 2), ("gates", gates, 2)):
+        _need(t, name, (torch.float32,), nd)
+    _need(state, "state", (torch.float32,))
+    for name, t in (("q_start", q_start), ("slots", slots), ("row_request", row_request)):
+        _need(t, name, _I, 1)
+    n, ld = proj.shape
+    channels, taps = conv_w.shape
+    heads = dt_bias.shape[0]
+    if out.shape != (n, channels) or gates.shape != (n, 2 * heads) or conv_b.shape[0] != channels \
+            or a_log.shape[0] != heads or conv_col + channels > ld or dt_col + heads > ld or row_request.shape[0] != n:
+        raise KernelError(f"conv_silu_gates: proj {tuple(proj.shape)}, conv {tuple(conv_w.shape)}, out "
+                          f"{tuple(out.shape)}, gates {tuple(gates.shape)}")
+    _check(_core(act).ib_conv_silu_gates(
+        _p(proj), ld, int(conv_col), channels, taps, _p(conv_w), _p(conv_b), _p(state), state[0].numel(),
+        int(conv_state_off), _p(q_start), _p(slots), _p(row_request), _p(out), int(dt_col), heads, _p(dt_bias),
+        _p(a_log), _p(gates), n, _stream()), "conv_silu_gates")
+
+
+def conv_state_shift(proj: torch.Tensor, conv_col: int, channels: int, taps: int, state: torch.Tensor,
+                     conv_state_off: int, q_start: torch.Tensor, slots: torch.Tensor, n_requests: int):
+    """After a step: every request's state keeps the last taps - 1 inputs of its convolution, oldest first."""
+    act = proj.dtype
+    _need(proj, "proj", _W, 2)
+    _need(state, "state", (torch.float32,))
+    _need(q_start, "q_start", _I, 1)
+    _need(slots, "slots", _I, 1)
+    if conv_col + channels > proj.shape[1] or state[0].numel() < conv_state_off + (taps - 1) * channels \
+            or q_start.shape[0] < n_requests + 1 or slots.shape[0] < n_requests:
+        raise KernelError(f"conv_state_shift: proj {tuple(proj.shape)}, {channels} channels of {taps} taps")
+    _check(_core(act).ib_conv_state_shift(_p(proj), proj.shape[1], int(conv_col), int(channels), int(taps), _p(state),
+                                          state[0].numel(), int(conv_state_off), _p(q_start), _p(slots),
+                                          int(n_requests), _stream()), "conv_state_shift")
+
+
+def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out: torch.Tensor):
+    """out = (y * silu(z)) with each of ``groups`` equal consecutive parts of the row divided by its root mean square,
+    times ``weight``: the gate comes before the norm.  ``y`` float32 [rows, inner]; ``z`` a [rows, inner] view of a
+    wider projection in the activation dtype."""
+    act = out.dtype
+    _need(y, "y", (torch.float32,), 2)
+    _need(weight, "weight", (torch.float32,), 1)
+    _need(out, "out", _W, 2)
+    n, inner = y.shape
+    if not (z.is_cuda and z.dtype == act and z.shape == (n, inner) and z.stride(1) == 1) or out.shape != (n, inner) \
+            or weight.shape[0] != inner or groups <= 0 or inner % groups:
+        raise KernelError(f"gate_group_norm: y {tuple(y.shape)}, z {tuple(z.shape)} {z.dtype}, {groups} parts")
+    _check(_core(act).ib_gate_group_norm(_p(y), _p(z), z.stride(0), _p(weight), int(groups), inner, float(eps), _p(out),
+                                         n, _stream()), "gate_group_norm")
+
+
+def clamped_gate(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float):
+    """out[r, j] = g sigmoid(slope g) (u + 1) with g = min(gate_up[r, j], limit) and
+    u = clamp(gate_up[r, inner + j], -limit, limit)."""
+    act = out.dtype
+    _need(gate_up, "gate_up", (act,), 2)
+    _need(out, "out", _W, 2)
+    n, inner = out.shape
+    if gate_up.shape != (n, 2 * inner):
+        raise KernelError(f"clamped_gate: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
+    _check(_core(act).ib_clamped_gate(_p(gate_up), _p(out), n, inner, float(limit), float(slope), _stream()),
+           "clamped_gate")
+
+
+def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], n_experts: int, top: int, has_shared: bool,
+                weights: torch.Tensor, act_dtype: torch.dtype):
+    """weights[r, e] = the softmax over the ``top`` largest of logits[r, :n_experts] + bias, among themselves, for
+    those experts and 0 for the others; with ``has_shared`` weights[r, n_experts] = sigmoid(logits[r, n_experts])."""
+    _need(logits, "logits", (torch.float32,), 2)
+    _need(bias, "bias", (torch.float32,), 1, optional=True)
+    _need(weights, "weights", (torch.float32,), 2)
+    n = logits.shape[0]
+    cols = n_experts + int(bool(has_shared))
+    if logits.shape[1] < cols or weights.shape != (n, cols) or (bias is not None and bias.shape[0] != n_experts) \
+            or not 0 < top <= n_experts:
+        raise KernelError(f"router_topk: logits {tuple(logits.shape)}, weights {tuple(weights.shape)}, top {top} of "
+                          f"{n_experts}")
+    _check(_core(act_dtype).ib_router_topk(_p(logits), logits.shape[1], _p(bias), int(n_experts), int(top),
+                                           int(bool(has_shared)), _p(weights), n, _stream()), "router_topk")
+
+
+def routed_gate(gate_up: torch.Tensor, weights: torch.Tensor, n_experts: int, ff: int, out: torch.Tensor):
+    """out[r, j] = silu(gate_up[r, j]) * gate_up[r, inner + j] * weights[r, e(j)], the experts' columns side by side:
+    e(j) = j / ff for the routed ones, n_experts for the columns after them (a shared expert)."""
+    act = out.dtype
+    _need(gate_up, "gate_up", (act,), 2)
+    _need(weights, "weights", (torch.float32,), 2)
+    _need(out, "out", _W, 2)
+    n, inner = out.shape
+    if gate_up.shape != (n, 2 * inner) or weights.shape[0] != n or n_experts * ff > inner \
+            or weights.shape[1] < n_experts + int(n_experts * ff < inner):
+        raise KernelError(f"routed_gate: gate_up {tuple(gate_up.shape)}, weights {tuple(weights.shape)}, out "
+                          f"{tuple(out.shape)}")
+    _check(_core(act).ib_routed_gate(_p(gate_up), _p(weights), weights.shape[1], int(n_experts), int(ff), _p(out), n,
+                                     inner, _stream()), "routed_gate")
+
+
+def decay_scan(x: torch.Tensor, q_col: int, k_col: int, v_col: int, groups: int, keep: torch.Tensor,
+               take: Optional[torch.Tensor], skip: Optional[torch.Tensor], state: torch.Tensor, q_start: torch.Tensor,
+               slots: torch.Tensor, n_requests: int, out: torch.Tensor, key_dim: int, act_dtype: torch.dtype,
+               max_rows: int = 0):
+    """A matrix state per head with a scalar decay, carried over each request's rows in float32:
+    S = keep S + take k v^T, o = S^T q + skip v.
+
+    ``x`` float32 [rows, ld] holds q and k as [groups, D] and v as [H, E] from the given columns on (head h reads
+    group h / (H / groups)); ``keep`` is [H] (one decay per head for all tokens) or a [rows, H] view with unit last
+    stride, ``take`` the same or None (1), ``skip`` [H] or None (0); ``out`` float32 [rows, H, E]; ``state`` float32
+    [slots, ...] with at least H*D*E numbers per slot, S first.  ``max_rows``: the most rows that a request brings, if
+    the caller knows (1: the form for steps of single tokens)."""
+    _need(x, "x", (torch.float32,), 2)
+    _need(out, "out", (torch.float32,), 3)
+    _need(state, "state", (torch.float32,))
+    _need(skip, "skip", (torch.float32,), 1, optional=True)
+    _need(q_start, "q_start", _I, 1)
+    _need(slots, "slots", _I, 1)
+    n, heads, e_dim = out.shape
+    d_dim = int(key_dim)
+
+    def per_token(t, name):
+        if t is None:
+            return None, 0
+        if not (t.is_cuda and t.dtype == torch.float32):
+            raise KernelError(f"decay_scan: {name} must be a float32 CUDA tensor")
+        if t.dim() == 1 and t.shape[0] == heads and t.stride(0) == 1:
+            return t.data_ptr(), 0
+        if t.dim() == 2 and t.shape == (n, heads) and t.stride(1) == 1:
+            return t.data_ptr(), t.stride(0)
+        raise KernelError(f"decay_scan: {name} must be [H] or a [rows, H] view with unit last stride, got "
+                          f"{tuple(t.shape)} with strides {t.stride()}")
+
+    keep_p, keep_ld = per_token(keep, "keep")
+    take_p, take_ld = per_token(take, "take")
+    if keep_p is None or x.shape[0] != n or groups <= 0 or heads % groups or d_dim <= 0 \
+            or max(q_col, k_col) + groups * d_dim > x.shape[1] or v_col + heads * e_dim > x.shape[1] \
+            or (skip is not None and skip.shape[0] != heads) \
+            or q_start.shape[0] < n_requests + 1 or slots.shape[0] < n_requests or state[0].numel() < heads * d_dim * e_dim:
+        raise KernelError(f"decay_scan: x {tuple(x.shape)}, out {tuple(out.shape)}, {groups} groups of {d_dim}")
+    if d_dim > 512:
+        raise KernelError(f"decay_scan: {d_dim} key channels per head are more than the kernel's 512")
+    _check(_core(act_dtype).ib_decay_scan(
+        _p(x), x.shape[1], int(q_col), int(k_col), int(v_col), int(groups), keep_p, keep_ld, take_p, take_ld, _p(skip),
+        _p(state), state[0].numel(), _p(q_start), _p(slots), int(n_requests), _p(out), heads, d_dim, e_dim,
+        int(max_rows), _stream()), "decay_scan")
+
+
 ARGMAX_CHUNK = 8192      # vocabulary entries per block of the two-stage argmax
 MMA_KEYS = 64          # keys per tile of the tensor-core attention kernel
 MMA_TARGET_CTAS = 1184  # four waves of 2 resident CTAs on 148 SMs: many small CTAs even out the last wave
@@ -1082,7 +1328,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     """
     n, nh, d = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
-    if not mma_attention_supported(q.dtype, nh, nkv, d, page_size):
+    if v_pages.shape[3] != d or not mma_attention_supported(q.dtype, nh, nkv, d, page_size):
         paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out)
         return
     # Prompt portions: tiles of 256 rows (two query tiles per CTA) where they still give every SM a CTA, else

@@ -31,20 +31,22 @@ class Attention:
 
     @staticmethod
     def declare(spec: AttentionSpec) -> List[TensorDecl]:
+        dv = spec.value_dim or spec.head_dim
         d = [TensorDecl(spec.q_proj, (spec.n_heads * spec.head_dim, spec.width)),
-             TensorDecl(spec.o_proj, (spec.width, spec.n_heads * spec.head_dim))]
+             TensorDecl(spec.o_proj, (spec.width, spec.n_heads * dv))]
         if spec.own_kv:
             d += [TensorDecl(spec.k_proj, (spec.n_kv_heads * spec.head_dim, spec.width)),
-                  TensorDecl(spec.v_proj, (spec.n_kv_heads * spec.head_dim, spec.width))]
-        if spec.q_norm is not None:
+                  TensorDecl(spec.v_proj, (spec.n_kv_heads * dv, spec.width))]
+        if spec.q_norm is not None and spec.q_norm.weight is not None:
             d.append(TensorDecl(spec.q_norm.weight, (spec.head_dim,), init="norm"))
-        if spec.k_norm is not None and spec.own_kv:
+        if spec.k_norm is not None and spec.k_norm.weight is not None and spec.own_kv:
             d.append(TensorDecl(spec.k_norm.weight, (spec.head_dim,), init="norm"))
         return d
 
     @staticmethod
     def cache_need(spec: AttentionSpec) -> Optional[KVNeed]:
-        return KVNeed(n_kv_heads=spec.n_kv_heads, head_dim=spec.head_dim, window=spec.window)
+        dv = spec.value_dim if spec.value_dim not in (None, spec.head_dim) else None
+        return KVNeed(n_kv_heads=spec.n_kv_heads, head_dim=spec.head_dim, window=spec.window, value_dim=dv)
 
     @staticmethod
     def state_need(spec: AttentionSpec):
@@ -64,15 +66,20 @@ class Attention:
                 raise ValueError(f"per-head norm must be an RMS norm over head_dim={spec.head_dim}, got {n}")
         if spec.q_norm is not None and spec.k_norm is not None and spec.q_norm.eps != spec.k_norm.eps:
             raise ValueError("query and key norms must share eps")
+        if spec.window and spec.chunk:
+            raise ValueError("an attention layer has a sliding window or chunks, not both")
         self.spec = spec
         self.rt = rt
+        self.value_dim = spec.value_dim or spec.head_dim
+        self.span = kernels.span_argument(spec.window, spec.chunk)     # which keys a token sees, as the kernels take it
         mats = [weights[spec.q_proj]]
         if spec.own_kv:
             mats += [weights[spec.k_proj], weights[spec.v_proj]]
         self.qkv = Linear(fuse_rows(mats), rt)
         self.o = Linear(weights[spec.o_proj], rt)
-        self.q_weight = weights[spec.q_norm.weight] if spec.q_norm is not None else None
-        self.k_weight = weights[spec.k_norm.weight] if (spec.k_norm is not None and spec.own_kv) else None
+        self.q_weight = weights[spec.q_norm.weight] if spec.q_norm is not None and spec.q_norm.weight else None
+        self.k_weight = weights[spec.k_norm.weight] \
+            if (spec.k_norm is not None and spec.k_norm.weight and spec.own_kv) else None
         if self.q_weight is not None and self.k_weight is not None and self.q_weight.dtype != self.k_weight.dtype:
             self.q_weight, self.k_weight = self.q_weight.float(), self.k_weight.float()
         self.eps = (spec.q_norm or spec.k_norm).eps if (spec.q_norm or spec.k_norm) else 0.0
@@ -99,9 +106,11 @@ class Attention:
         q = torch.empty((n, s.n_heads, s.head_dim), dtype=self.rt.dtype, device=h.device)
         kernels.qk_norm_rope_store(qkv, s.n_heads, s.n_kv_heads, s.head_dim, s.own_kv, self.q_weight, self.k_weight,
                                    self.eps, self.cos, self.sin, self.rot_dim, ctx.positions, ctx.row_request,
-                                   table, k_pages, v_pages, q, interleaved=self.interleaved)
-        out = torch.empty((n, s.n_heads * s.head_dim), dtype=self.rt.dtype, device=h.device)
-        kernels.paged_attention(q, k_pages, v_pages, table, ctx, s.scale, s.window, out)
+                                   table, k_pages, v_pages, q, interleaved=self.interleaved,
+                                   norm_q=s.q_norm is not None, norm_k=s.k_norm is not None and s.own_kv,
+                                   norm_after_rotation=s.norm_after_rotation)
+        out = torch.empty((n, s.n_heads * self.value_dim), dtype=self.rt.dtype, device=h.device)
+        kernels.paged_attention(q, k_pages, v_pages, table, ctx, s.scale, self.span, out)
         return self.o(out, sink=sink)
 
 

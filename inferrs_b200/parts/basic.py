@@ -1,6 +1,7 @@
 """Norm, position encoding and the matrix product that the other parts are made of."""
 from __future__ import annotations
 
+import math
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -9,6 +10,12 @@ from .. import kernels
 from ..runtime import Runtime
 from .registry import register_norm, register_position
 from .spec import NormSpec, PositionSpec, TensorDecl
+
+
+def _nothing_pending(delta):
+    """A block that norms after the sum hands on a copy of the stream instead of an output that is still to be
+    added (an object with ``rows`` and no ``delta``): for a norm that means that nothing is pending."""
+    return None if (delta is not None and hasattr(delta, "rows") and not hasattr(delta, "delta")) else delta
 
 
 class StreamUpdate:
@@ -34,12 +41,15 @@ class RMSNorm:
         return [TensorDecl(spec.weight, (spec.size,), init="norm")]
 
     def __init__(self, spec: NormSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        if spec.weight is None:
+            raise ValueError("a norm of the residual stream needs a weight")
         self.spec = spec
         self.rt = rt
         self.weight = weights[spec.weight]
 
     def add_norm(self, residual: torch.Tensor, delta, rows: Optional[torch.Tensor] = None,
                  read: Optional[torch.Tensor] = None):
+        delta = _nothing_pending(delta)
         groups = getattr(self.spec, "groups", 1)
         if residual.dim() == 3 or groups != 1 or isinstance(delta, StreamUpdate) or read is not None:
             streams = residual if residual.dim() == 3 else residual.unsqueeze(1)
@@ -90,6 +100,7 @@ class NoNorm:
 
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        delta = _nothing_pending(delta)
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, residual.shape[1]), dtype=self.rt.dtype, device=residual.device)
         kernels.add_cast(residual, delta, out, rows)
@@ -132,6 +143,42 @@ class RotaryInterleaved(RotarySplitHalf):
     interleaved = True
 
 
+class RotaryScaled:
+    """Pairs as in :class:`RotarySplitHalf`; the frequencies, the stretch of the slow pairs for long contexts and the
+    factor on cos and sin are those of :class:`~inferrs_b200.parts.spec.PositionSpec` with ``scaling``.  Frequencies
+    and angles are made in float64 on the host and the tables rounded to float32 once."""
+
+    def __init__(self, spec: PositionSpec, rt: Runtime):
+        if spec.rot_dim <= 0 or spec.rot_dim % 2:
+            raise ValueError(f"rot_dim must be positive and even, got {spec.rot_dim}")
+        if spec.max_positions <= 0 or not spec.theta > 1.0:
+            raise ValueError(f"max_positions must be positive and theta above 1, got {spec.max_positions}, {spec.theta}")
+        self.spec = spec
+        dims = spec.rot_dim
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        freq = float(spec.theta) ** (-2.0 * i / dims)
+        magnitude = 1.0
+        if spec.scaling is not None:
+            factor, original, fast, slow = (float(v) for v in spec.scaling)
+            if not (factor > 0 and original > 0 and fast > 0 and slow > 0):
+                raise ValueError(f"the scaling's factor, original length, fast and slow turns must be positive: {spec.scaling}")
+
+            def turns(t: float) -> float:      # the pair that makes t turns over the original context
+                return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(float(spec.theta)))
+
+            lo = max(math.floor(turns(fast)), 0)
+            hi = min(math.ceil(turns(slow)), dims - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            freq = freq / factor * ramp + freq * (1.0 - ramp)
+            magnitude = 0.1 * math.log(factor) + 1.0
+        angle = torch.arange(spec.max_positions, dtype=torch.float64)[:, None] * freq[None, :]
+        self.cos = (torch.cos(angle) * magnitude).to(torch.float32).contiguous().to(rt.device)
+        self.sin = (torch.sin(angle) * magnitude).to(torch.float32).contiguous().to(rt.device)
+
+    def tables(self):
+        return self.cos, self.sin, self.spec.rot_dim
+
+
 class NoPosition:
     def __init__(self, spec: PositionSpec, rt: Runtime):
         self.spec = spec
@@ -142,6 +189,7 @@ class NoPosition:
 
 register_position("rotary_split_half", RotarySplitHalf)
 register_position("rotary_interleaved", RotaryInterleaved)
+register_position("rotary_scaled", RotaryScaled)
 register_position("none", NoPosition)
 
 

@@ -5,6 +5,7 @@ from typing import List, Optional
 
 import torch
 
+from .. import kernels
 from .basic import StreamUpdate
 from .registry import register_arrangement
 from .spec import TensorDecl
@@ -14,8 +15,9 @@ class BuiltSubLayer:
     """A sub-layer whose parts are built: ``part`` with its ``category`` ("mixer" or "feed_forward"),
     the ``norm`` before it and the ``post_norm`` after it (either may be None)."""
 
-    def __init__(self, category: str, part, norm=None, post_norm=None):
+    def __init__(self, category: str, part, norm=None, post_norm=None, sum_norm=None):
         self.category, self.part, self.norm, self.post_norm = category, part, norm, post_norm
+        self.sum_norm = sum_norm     # the norm of the stream itself after this sub-layer (norm_after_sum blocks)
 
     def run(self, ctx, cache_id: int, h, sink=None):
         kw = {} if sink is None else {"sink": sink}
@@ -141,3 +143,64 @@ class HyperConnectionBlock:
 
 
 register_arrangement("hyper_connections", HyperConnectionBlock)
+
+
+class StreamCopy:
+    """What a block that norms after the sum hands on in place of a pending output: nothing is left to add, and
+    ``rows`` holds the stream as it stands, in the activation dtype, for whoever reads the stream itself next."""
+
+    def __init__(self, rows: torch.Tensor):
+        self.rows = rows
+
+
+class NormAfterSumBlock:
+    """For every sub-layer in turn: x <- norm(scale * x + part(x)), with ``scale`` the layer's ``residual_scale``
+    and ``norm`` the sub-layer's ``sum_norm``.  The parts read the stream itself, and the stream itself is
+    normalised: float32, in place, by one kernel that also writes the copy in the activation dtype that the next
+    part reads.  A sub-layer without a part contributes nothing to its sum.
+
+    The block hands on a :class:`StreamCopy` (the next block of this kind reads it instead of casting the stream
+    again); a pending output from a block of another kind is added first.
+    """
+
+    def __init__(self, spec, sublayers: List[BuiltSubLayer]):
+        if not sublayers:
+            raise ValueError("a layer needs at least one sub-layer")
+        for s in sublayers:
+            if s.sum_norm is None or s.post_norm is not None or not isinstance(s.norm, _no_norm()):
+                raise ValueError("a sub-layer of a block that norms after the sum has a sum_norm and no other norm")
+            if getattr(s.sum_norm.spec, "groups", 1) != 1:
+                raise ValueError("the norm after the sum is a plain RMS norm (no groups)")
+        self.spec = spec
+        self.sublayers = list(sublayers)
+        self.scale = float(spec.residual_scale)
+        # norm weights as float32, once
+        self.weights = [s.sum_norm.weight.to(torch.float32).contiguous() for s in sublayers]
+
+    def parts(self):
+        for s in self.sublayers:
+            if s.part is not None:
+                yield s.part
+            yield s.sum_norm
+
+    def forward(self, ctx, cache_id: int, residual: torch.Tensor, pending):
+        if residual.dim() != 2:
+            raise ValueError("a block that norms after the sum runs on the plain residual [rows, width]")
+        rt_dtype = self.sublayers[0].sum_norm.rt.dtype
+        if isinstance(pending, StreamCopy):
+            h = pending.rows
+        else:
+            h = self.sublayers[0].norm.add_norm(residual, pending)      # adds what is pending; the stream as act rows
+        for s, w in zip(self.sublayers, self.weights):
+            y = s.run(ctx, cache_id, h) if s.part is not None else None
+            h = torch.empty(residual.shape, dtype=rt_dtype, device=residual.device)
+            kernels.scaled_add_norm(residual, y, self.scale, w, s.sum_norm.spec.eps, h, rt_dtype)
+        return StreamCopy(h)
+
+
+def _no_norm():
+    from .basic import NoNorm
+    return NoNorm
+
+
+register_arrangement("norm_after_sum", NormAfterSumBlock)

@@ -1,6 +1,6 @@
 """Mixers that carry a matrix state per head from token to token instead of a cache of keys and values.
 
-Both keep, per request, a float32 state of fixed size in the cache's state slots (one slot per live request, zeroed
+All keep, per request, a float32 state of fixed size in the cache's state slots (one slot per live request, zeroed
 when a request takes it) and walk a request's rows in order inside one kernel, so a prompt may be cut anywhere and
 a portion may stand beside single tokens of other requests.
 
@@ -15,9 +15,9 @@ import torch
 from .. import kernels
 from ..cache.storage import StateNeed
 from ..runtime import Runtime
-from .basic import Linear, fuse_rows
+from .basic import Linear, build_position, fuse_rows
 from .registry import register_mixer
-from .spec import ChannelDecayScanSpec, ScalarGateScanSpec, TensorDecl
+from .spec import ChannelDecayScanSpec, FixedDecayScanSpec, ScalarGateScanSpec, StateSpaceScanSpec, TensorDecl
 
 
 class _ScanMixer:
@@ -120,5 +120,134 @@ class ScalarGateScan(_ScanMixer):
                          kernels.GATE_SIGMOID)
 
 
+class FixedDecayScan:
+    """Retention (see :class:`~inferrs_b200.parts.spec.FixedDecayScanSpec`).  One product gives q, k, v and the gate;
+    q and k are rotated (k also scaled) into float32 rows, the scan with one constant decay per head runs on those,
+    and the per-head division by the root mean square with the silu gate is one kernel before the output product."""
+
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec: FixedDecayScanSpec) -> List[TensorDecl]:
+        hd, he = spec.n_heads * spec.key_dim, spec.n_heads * spec.value_dim
+        return [TensorDecl(spec.q_proj, (hd, spec.width)), TensorDecl(spec.k_proj, (hd, spec.width)),
+                TensorDecl(spec.v_proj, (he, spec.width)), TensorDecl(spec.gate_proj, (he, spec.width)),
+                TensorDecl(spec.o_proj, (spec.width, he))]
+
+    @staticmethod
+    def cache_need(spec):
+        return None
+
+    @staticmethod
+    def state_need(spec: FixedDecayScanSpec) -> Optional[StateNeed]:
+        return StateNeed(shape=(spec.n_heads * spec.key_dim * spec.value_dim,))
+
+    def __init__(self, spec: FixedDecayScanSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        if len(spec.decay) != spec.n_heads or any(not 0.0 < float(a) <= 1.0 for a in spec.decay):
+            raise ValueError(f"a fixed-decay scan needs one decay in (0, 1] per head, got {spec.decay} for "
+                             f"{spec.n_heads} heads")
+        self.spec, self.rt = spec, rt
+        hd, he = spec.n_heads * spec.key_dim, spec.n_heads * spec.value_dim
+        self.qkvg = Linear(fuse_rows([weights[spec.q_proj], weights[spec.k_proj], weights[spec.v_proj],
+                                      weights[spec.gate_proj]]), rt)
+        self.gate_col = 2 * hd + he
+        self.o = Linear(weights[spec.o_proj], rt)
+        self.decay = torch.tensor([float(a) for a in spec.decay], dtype=torch.float64).to(torch.float32).to(rt.device)
+        self.cos, self.sin, self.rot_dim = build_position(spec.position, rt).tables()
+        if self.rot_dim > spec.key_dim:
+            raise ValueError(f"rot_dim {self.rot_dim} exceeds the key size {spec.key_dim}")
+        # q, k and v of a row as float32, side by side
+        self.slices = ((0, 0, spec.n_heads, spec.key_dim, 1, 1.0),
+                       (hd, hd, spec.n_heads, spec.key_dim, 1, float(spec.key_dim) ** -0.5),
+                       (2 * hd, 2 * hd, spec.n_heads, spec.value_dim, 0, 1.0))
+
+    def forward(self, ctx, cache_id: int, h):
+        s = self.spec
+        n = h.shape[0]
+        hd, he = s.n_heads * s.key_dim, s.n_heads * s.value_dim
+        proj = self.qkvg(h)
+        x = torch.empty((n, 2 * hd + he), dtype=torch.float32, device=h.device)
+        kernels.heads_to_float(proj, self.slices, x, self.cos, self.sin, self.rot_dim, ctx.positions)
+        o = torch.empty((n, s.n_heads, s.value_dim), dtype=torch.float32, device=h.device)
+        kernels.decay_scan(x, 0, hd, 2 * hd, s.n_heads, self.decay, None, None, ctx.storage.state(cache_id), ctx.q_start,
+                           ctx.slots, ctx.n_requests, o, s.key_dim, self.rt.dtype, max_rows=ctx.max_q_len)
+        gated = torch.empty((n, he), dtype=self.rt.dtype, device=h.device)
+        kernels.head_norm_gate(o, proj[:, self.gate_col:], None, True, kernels.GATE_SILU, s.eps, gated)
+        return self.o(gated)
+
+
+class StateSpaceScan:
+    """The state-space mixer of Mamba-2 (see :class:`~inferrs_b200.parts.spec.StateSpaceScanSpec`).  One product gives
+    z, x, B, C and dt; one kernel does the short convolution with silu (reading what the state keeps of earlier
+    steps) and turns dt into what the scan keeps and takes; the scan runs in float32 with B as keys, C as queries and
+    x as values; gate, norm in parts and weight are one kernel before the output product.  The state of a slot is the
+    matrices [H, state, value_dim] and then the convolution's last taps - 1 inputs [taps - 1, channels], float32."""
+
+    graph_safe = True
+
+    @staticmethod
+    def _sizes(spec: StateSpaceScanSpec):
+        inner = spec.n_heads * spec.value_dim
+        return inner, inner + 2 * spec.groups * spec.state      # the gate's columns, the convolution's channels
+
+    @staticmethod
+    def declare(spec: StateSpaceScanSpec) -> List[TensorDecl]:
+        inner, channels = StateSpaceScan._sizes(spec)
+        return [TensorDecl(spec.in_proj, (inner + channels + spec.n_heads, spec.width)),
+                TensorDecl(spec.conv, (channels, spec.taps), init="uniform:0:0.5"),
+                TensorDecl(spec.conv_bias, (channels,), init="uniform:0:0.1"),
+                TensorDecl(spec.dt_bias, (spec.n_heads,), init="uniform:-2:1"),
+                TensorDecl(spec.a_log, (spec.n_heads,), init="uniform:0:1"),
+                TensorDecl(spec.skip, (spec.n_heads,), init="uniform:1:0.2"),
+                TensorDecl(spec.out_norm, (inner,), init="norm"),
+                TensorDecl(spec.o_proj, (spec.width, inner))]
+
+    @staticmethod
+    def cache_need(spec):
+        return None
+
+    @staticmethod
+    def state_need(spec: StateSpaceScanSpec) -> Optional[StateNeed]:
+        _, channels = StateSpaceScan._sizes(spec)
+        return StateNeed(shape=(spec.n_heads * spec.state * spec.value_dim + (spec.taps - 1) * channels,))
+
+    def __init__(self, spec: StateSpaceScanSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        if spec.n_heads % spec.groups or (spec.n_heads * spec.value_dim) % spec.norm_groups or spec.taps < 1:
+            raise ValueError(f"a state-space mixer needs heads that divide into its groups, an inner size that divides "
+                             f"into the norm's parts and at least one tap, got {spec}")
+        self.spec, self.rt = spec, rt
+        self.inner, self.channels = self._sizes(spec)
+        self.in_proj = Linear(weights[spec.in_proj], rt)
+        self.o = Linear(weights[spec.o_proj], rt)
+        f32 = lambda name: weights[name].to(torch.float32).contiguous()     # noqa: E731
+        self.conv, self.conv_bias = f32(spec.conv), f32(spec.conv_bias)
+        self.dt_bias, self.a_log, self.skip, self.out_norm = (f32(spec.dt_bias), f32(spec.a_log), f32(spec.skip),
+                                                              f32(spec.out_norm))
+        self.conv_state_off = spec.n_heads * spec.state * spec.value_dim
+
+    def forward(self, ctx, cache_id: int, h):
+        s = self.spec
+        n = h.shape[0]
+        gn = s.groups * s.state
+        proj = self.in_proj(h)
+        state = ctx.storage.state(cache_id)
+        xbc = torch.empty((n, self.channels), dtype=torch.float32, device=h.device)
+        gates = torch.empty((n, 2 * s.n_heads), dtype=torch.float32, device=h.device)
+        kernels.conv_silu_gates(proj, self.inner, self.conv, self.conv_bias, state, self.conv_state_off, ctx.q_start,
+                                ctx.slots, ctx.row_request, xbc, self.inner + self.channels, self.dt_bias, self.a_log,
+                                gates)
+        kernels.conv_state_shift(proj, self.inner, self.channels, s.taps, state, self.conv_state_off, ctx.q_start,
+                                 ctx.slots, ctx.n_requests)
+        y = torch.empty((n, s.n_heads, s.value_dim), dtype=torch.float32, device=h.device)
+        kernels.decay_scan(xbc, self.inner + gn, self.inner, 0, s.groups, gates[:, :s.n_heads], gates[:, s.n_heads:],
+                           self.skip, state, ctx.q_start, ctx.slots, ctx.n_requests, y, s.state, self.rt.dtype,
+                           max_rows=ctx.max_q_len)
+        gated = torch.empty((n, self.inner), dtype=self.rt.dtype, device=h.device)
+        kernels.gate_group_norm(y.view(n, self.inner), proj[:, :self.inner], self.out_norm, s.norm_groups, s.eps, gated)
+        return self.o(gated)
+
+
 register_mixer("channel_decay_scan", ChannelDecayScan)
+register_mixer("fixed_decay_scan", FixedDecayScan)
+register_mixer("state_space_scan", StateSpaceScan)
 register_mixer("scalar_gate_scan", ScalarGateScan)

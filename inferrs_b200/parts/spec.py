@@ -34,11 +34,12 @@ class TensorDecl:
 @dataclass(frozen=True)
 class NormSpec:
     """x / sqrt(mean(x^2) + eps) * weight.  ``groups`` > 1: the row is cut into that many equal consecutive parts
-    and each part is divided by its own root mean square."""
+    and each part is divided by its own root mean square.  ``weight`` None (where a part allows it: the per-head
+    norms of attention): the division alone."""
 
     size: int
     eps: float
-    weight: str
+    weight: Optional[str]
     kind: str = "rms"
     groups: int = 1
 
@@ -49,13 +50,18 @@ class PositionSpec:
 
     ``kind="rotary_split_half"`` pairs element ``i`` with ``i + rot_dim/2``;
     ``kind="rotary_interleaved"`` pairs element ``2i`` with ``2i + 1``;
-    ``kind="none"`` leaves heads as they are.
+    ``kind="none"`` leaves heads as they are.  ``kind="rotary_scaled"`` pairs like ``rotary_split_half`` and stretches
+    the slow pairs for contexts longer than the ``original`` one (``scaling`` = (factor, original, fast, slow): with
+    turns(t) = rot_dim ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(turns(fast)), 0),
+    hi = min(ceil(turns(slow)), rot_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at
+    f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1).
     """
 
     kind: str = "rotary_split_half"
     rot_dim: int = 0
     theta: float = 0.0
     max_positions: int = 0
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -63,9 +69,11 @@ class AttentionSpec:
     """Grouped-query attention over a paged cache of keys and values.
 
     ``window``: a query at position i sees keys j with i - window < j <= i;
-    ``None`` means all keys j <= i.  ``own_kv=False`` describes a layer that
-    has no key/value projections and reads the cache that another schedule
-    entry writes.
+    ``None`` means all keys j <= i.  ``chunk``: a query sees only the keys of its own chunk of that many positions,
+    counted from position 0 of the sequence (floor(i / chunk) = floor(j / chunk)).  ``own_kv=False`` describes a
+    layer that has no key/value projections and reads the cache that another schedule
+    entry writes.  ``value_dim``: the size of a value head where it differs from ``head_dim``.
+    ``norm_after_rotation``: the per-head norms of queries and keys come after the rotation instead of before it.
     """
 
     width: int
@@ -83,11 +91,15 @@ class AttentionSpec:
     window: Optional[int] = None
     own_kv: bool = True
     kind: str = "attention"
+    value_dim: Optional[int] = None
+    chunk: Optional[int] = None
+    norm_after_rotation: bool = False
 
 
 @dataclass(frozen=True)
 class GatedDenseSpec:
-    """down( act(gate(x)) * up(x) )."""
+    """down( act(gate(x)) * up(x) ).  ``activation="clamped_swish"``: with g = min(gate(x), limit) and
+    u = clamp(up(x), -limit, limit) the inner rows are g sigmoid(slope g) (u + 1)."""
 
     width: int
     inner: int
@@ -96,6 +108,78 @@ class GatedDenseSpec:
     down_proj: str
     activation: str = "silu"
     kind: str = "gated_dense"
+    limit: Optional[float] = None
+    slope: float = 1.702
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of small gated feed-forwards.  Router logits z = router(x) + router_bias in float32; the ``top``
+    experts with the largest logits are chosen and weighed by the softmax over the chosen logits alone; the output is
+    the weighted sum of down_e( silu(gate_e(x)) * up_e(x) ) over the chosen.  ``experts`` names every expert's
+    (gate, up, down) tensors.  ``shared`` (optional, (gate, up, down, gate vector) with ``shared_inner``): an expert
+    that runs for every token and is added times sigmoid(gate_vector . x)."""
+
+    width: int
+    inner: int
+    top: int
+    router: str
+    router_bias: Optional[str]
+    experts: Tuple[Tuple[str, str, str], ...]
+    shared: Optional[Tuple[str, str, str, str]] = None
+    shared_inner: int = 0
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
+class FixedDecayScanSpec:
+    """Retention: linear attention with a fixed decay per head and neither softmax nor denominator.  Per head a
+    matrix state S [key_dim, value_dim], S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t; q and k are rotated by
+    position (``position``), k is then multiplied by key_dim^(-1/2); each head's o is divided by its root mean square
+    (no weight); the heads times silu(gate(x)) go through ``o_proj``."""
+
+    width: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]
+    eps: float
+    position: PositionSpec
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    o_proj: str
+    kind: str = "fixed_decay_scan"
+
+
+@dataclass(frozen=True)
+class StateSpaceScanSpec:
+    """The state-space mixer of Mamba-2.  ``in_proj`` gives [z: inner | x: inner | B: groups*state | C: groups*state |
+    dt: n_heads] with inner = n_heads * value_dim.  x, B and C pass a causal convolution per channel (``conv``
+    [channels, taps] with ``conv_bias``; the last tap is the current token's) and silu; dt = softplus(dt + dt_bias).
+    Per head (head h reads group h / (n_heads / groups)) a state S [state, value_dim]:
+    S_t = exp(-exp(a_log_h) dt) S_{t-1} + dt B_t x_t^T, y_t = S_t^T C_t + skip_h x_t.  y times silu(z) is divided by
+    its root mean square in ``norm_groups`` equal parts, multiplied by ``out_norm`` and goes through ``o_proj``.  The
+    last taps - 1 inputs of the convolution are part of the state."""
+
+    width: int
+    n_heads: int
+    value_dim: int
+    state: int
+    groups: int
+    taps: int
+    norm_groups: int
+    eps: float
+    in_proj: str
+    conv: str
+    conv_bias: str
+    dt_bias: str
+    a_log: str
+    skip: str
+    out_norm: str
+    o_proj: str
+    kind: str = "state_space_scan"
 
 
 @dataclass(frozen=True)
@@ -224,6 +308,8 @@ class SubLayerSpec:
     post_norm: Optional[Any] = None
     # for arrangements whose sub-layers hang on the residual in a way of their own (StreamConnectionSpec)
     connection: Optional[Any] = None
+    # for the arrangement that norms after the sum: the norm of the stream itself once the part's output is in it
+    sum_norm: Optional[Any] = None
 
 
 @dataclass(frozen=True)
@@ -234,10 +320,14 @@ class LayerSpec:
     pre-norm block of a mixer and a feed-forward is two sub-layers with a ``norm`` each
     (:func:`pre_norm_layer`); a block with four norms gives both a ``post_norm`` too; a block of a
     mixer alone has one sub-layer.
+
+    ``arrangement="norm_after_sum"``: for every sub-layer in turn, x <- sum_norm(residual_scale * x + part(x)): the
+    parts read the stream itself, and the stream itself is normalised (``part`` None: the sum is residual_scale * x).
     """
 
     sublayers: Tuple[SubLayerSpec, ...]
     arrangement: str = "sequential"
+    residual_scale: float = 1.0
 
     def parts_of(self, category: str) -> Tuple[Any, ...]:
         return tuple(s.part for s in self.sublayers if s.category == category)
@@ -259,12 +349,12 @@ class LayerSpec:
             if s.category == category:
                 if seen == index:
                     s = SubLayerSpec(part=part, category=category, norm=s.norm, post_norm=s.post_norm,
-                                     connection=s.connection)
+                                     connection=s.connection, sum_norm=s.sum_norm)
                 seen += 1
             subs.append(s)
         if seen <= index:
             raise ValueError(f"the layer has {seen} sub-layers of category '{category}', none with index {index}")
-        return LayerSpec(sublayers=tuple(subs), arrangement=self.arrangement)
+        return LayerSpec(sublayers=tuple(subs), arrangement=self.arrangement, residual_scale=self.residual_scale)
 
 
 def pre_norm_layer(mixer_norm: Any, mixer: Any, ffn_norm: Any, ffn: Any) -> LayerSpec:
@@ -300,6 +390,8 @@ class ModelSpec:
     max_positions: int
     # embedding rows are multiplied by this as they are gathered (None: not at all)
     embedding_scale: Optional[float] = None
+    # a norm on the embedding rows before the first layer (None: none)
+    embedding_norm: Optional[Any] = None
     # logits are multiplied by logit_scale and then squashed to cap * tanh(x / cap) (None: neither)
     logit_scale: Optional[float] = None
     logit_softcap: Optional[float] = None
