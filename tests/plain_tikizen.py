@@ -197,6 +197,18 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
         if mlp is not None:
             y = dense_ff(x, mlp, w, f"l{i}.mlp") if mlp["kind"] == "dense" else moe_ff(x, mlp, w, f"l{i}.mlp")
             x = rms_norm(alpha * x + y, w[f"l{i}.norm2"], eps)
+        elif f"l{i}.norm2" in w:       # no feed-forward, but the second norm is there: its sum is alpha x alone
+            x = rms_norm(alpha * x, w[f"l{i}.norm2"], eps)
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt: List[int], n_new: int, dtype=torch.float32) -> List[int]:
+    """The tokens that always taking the largest logit gives (the whole sequence is run again for every token)."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(torch.argmax(forward(config, weights, toks, dtype)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
