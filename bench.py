@@ -20,6 +20,13 @@ is another workload (the default one stays as it is): prefill and decode through
 sizes that resemble a real model's layers, random weights, beside the Qwen3 shape of equal width, heads, head size,
 layers and feed-forward parameters, and the design's own kernels alone (the scans with a matrix state, the attention
 over cached latents) beside the Qwen3 attention kernels at equal sizes, each with its fraction of the measured peaks.
+
+    python bench.py --design tikizen [--design-layers N]
+
+does the same for the Tikizen design (attention in chunks, the state-space mixer, retention, attention on another
+layer's keys and values; a dense feed-forward and routed experts) beside the Vebonex design, the closest existing
+model (scans with a matrix state beside attention, per-request state slots beside pages), at equal width, heads,
+layers and feed-forward parameters, and its scan beside Vebonex's scans.
 """
 from __future__ import annotations
 
@@ -191,6 +198,32 @@ def vebonex_config(width: int, heads: int, ff: int, q_rank: int, kv_rank: int, n
             "norm": {"eps": 1e-5, "groups": 4}, "layers": [layer(i) for i in range(n_layers)]}
 
 
+def tikizen_config(width: int, heads: int, ff: int, n_layers: int, vocab: int) -> dict:
+    """Layers in the order attention in chunks, state-space mixer, retention, attention on the first one's keys and
+    values, repeated; a dense feed-forward after the attention layers, eight routed experts of ff / 8 (two chosen) and
+    a shared one after the others."""
+    rot = {"base": 1e6, "dims": 128, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+
+    def layer(i):
+        kind = i % 4
+        dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+        moe = {"kind": "moe", "expert": {"ff": ff // 8}, "router": {"experts": 8, "top": 2}, "shared": {"ff": ff // 8}}
+        if kind in (0, 3):
+            m = {"heads": heads, "kv_heads": heads // 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot,
+                 "mask": {"size": 1024}}
+            if kind == 3:
+                m["kv_from"] = i - 3
+            return {"type": "attention", "mixer": m, "mlp": dense}
+        if kind == 1:
+            return {"type": "mamba2", "mixer": {"heads": heads, "vdim": 128, "state": 128, "groups": heads // 8 or 1,
+                                                "conv": 4, "norm_groups": 2}, "mlp": moe}
+        return {"type": "retention", "mixer": {"heads": heads, "dim": 128, "vdim": 128,
+                                               "decay": [1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)],
+                                               "rot": {"base": 1e6, "dims": 128}}, "mlp": moe}
+    return {"architecture": "Tikizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
+            "max_positions": 8192, "layers": [layer(i) for i in range(n_layers)]}
+
+
 def design_bench(args) -> int:
     import argparse as ap_
     import gc
@@ -255,6 +288,35 @@ def design_bench(args) -> int:
                 "decode_ms_per_step": round(dms, 4), "decode_tok_s": round(batch * 1e3 / dms, 1),
                 "launches_per_decode_step": round(launches, 1)}
 
+    def ns(**kw):
+        return ap_.Namespace(iters=20, page_size=16, dtype="bf16", **kw)
+
+    def fractions(r):
+        r["frac_hbm"] = round(r["GBps"] / pk["hbm_gbs"], 4)
+        r["frac_bf16"] = round(r["TFLOPs"] / pk["bf16_tflops"], 4)
+        return r
+
+    if args.design == "tikizen":
+        sizes = []
+        for name, width, heads, ff in (("width 2048", 2048, 16, 8192), ("width 4096", 4096, 32, 16384)):
+            n_layers = args.design_layers
+            ours = measure(tikizen_config(width, heads, ff, n_layers, vocab))
+            closest = measure(vebonex_config(width, heads, ff, 768 * width // 2048, 512, n_layers, vocab, positions))
+            sizes.append({"size": name, "layers": n_layers, "heads": heads, "ff": ff, "tikizen": ours,
+                          "vebonex_equal_size": closest})
+        rows = []
+        for heads in (16, 32):
+            for mode, groups in (("scalar", 0), ("scalar", max(heads // 8, 1)), ("decay", 0), ("gates", 0)):
+                rows.append(microbench.scan(ns(mode=mode, groups=groups, form="prefill", batch=1, tokens=2048, heads=heads,
+                                               key_dim=128, value_dim=128)))
+                for b in (8, 64):
+                    rows.append(microbench.scan(ns(mode=mode, groups=groups, form="decode", batch=b, tokens=1, heads=heads,
+                                                   key_dim=128, value_dim=128)))
+        print(json.dumps({"design": "Tikizen", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights",
+                          "prompt_len": PROMPT_LEN, "decode_batch": batch, "decode_steps": args.design_steps,
+                          "peaks": pk, "sizes": sizes, "kernels": [fractions(r) for r in rows]}))
+        return 0
+
     sizes = []
     for name, width, heads, ff, q_rank, kv_rank in (("width 2048", 2048, 16, 8192, 768, 512),
                                                     ("width 4096", 4096, 32, 16384, 1536, 512)):
@@ -270,13 +332,6 @@ def design_bench(args) -> int:
                       "vebonex": ours, "qwen3_equal_size": closest})
 
     # the design's own kernels alone, and the closest model's attention kernels at equal sizes
-    def ns(**kw):
-        return ap_.Namespace(iters=20, page_size=16, dtype="bf16", **kw)
-
-    def fractions(r):
-        r["frac_hbm"] = round(r["GBps"] / pk["hbm_gbs"], 4)
-        r["frac_bf16"] = round(r["TFLOPs"] / pk["bf16_tflops"], 4)
-        return r
     rows = []
     for heads in (16, 32):
         for mode in ("gates", "decay"):
@@ -307,7 +362,8 @@ def main() -> int:
     ap.add_argument("--clock-interval-ms", type=int, default=200, help="how often nvidia-smi is asked for the clocks")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points and the prefill")
     ap.add_argument("--no-workloads", action="store_true", help="skip the Qwen3-0.6B and Qwen3-32B workloads")
-    ap.add_argument("--design", choices=["vebonex"], help="another workload: this design beside the closest model")
+    ap.add_argument("--design", choices=["vebonex", "tikizen"],
+                    help="another workload: this design beside the closest model")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of both models of --design")
     ap.add_argument("--design-steps", type=int, default=64, help="timed decode steps of --design")
     args = ap.parse_args()

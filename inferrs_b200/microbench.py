@@ -148,6 +148,8 @@ def scan(args) -> dict:
     dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
     lens = [args.tokens] if args.form == "prefill" else [1] * args.batch
     n = sum(lens)
+    if args.mode == "scalar":
+        return _scalar_decay_scan(args, lens, dtype)
     ld = 2 * h * d + 2 * h * e
     proj = torch.randn(n, ld, device=dev).to(dtype)
     mode = kernels.SCAN_CHANNEL_DECAY if args.mode == "decay" else kernels.SCAN_SCALAR_GATES
@@ -166,6 +168,29 @@ def scan(args) -> dict:
     byts = n * (2 * h * d + h * e) * el + n * gw * 4 + n * h * e * 4 + 2 * len(lens) * n_state * 4
     flops = 4 * n * h * d * e
     return {"kernel": f"scan/{args.mode}/{args.form}", "heads": h, "key_dim": d, "value_dim": e, "rows": n,
+            "requests": len(lens), "us": round(us, 2), "GBps": round(byts / us / 1e3, 1),
+            "TFLOPs": round(flops / us / 1e6, 2), "us_per_token": round(us / max(lens), 4)}
+
+
+def _scalar_decay_scan(args, lens, dtype) -> dict:
+    """The scan with one decay per (token, head) alone (retention, the state-space mixer): float32 rows of q, k
+    (shared by the ``groups`` heads of a group) and v, a keep and a take per token and head.  Bytes: those rows, the
+    result, and every touched state read and written once."""
+    h, d, e, g = args.heads, args.key_dim, args.value_dim, getattr(args, "groups", 0) or args.heads
+    dev = torch.device("cuda")
+    n = sum(lens)
+    x = torch.randn(n, 2 * g * d + h * e, device=dev)
+    gates = torch.rand(n, 2 * h, device=dev) * 0.1 + 0.9
+    state = torch.zeros(len(lens) + 1, h * d * e, device=dev)
+    q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+    out = torch.empty(n, h, e, dtype=torch.float32, device=dev)
+    fn = lambda: kernels.decay_scan(x, 0, g * d, 2 * g * d, g, gates[:, :h], gates[:, h:], None, state, q_start,  # noqa: E731
+                                    slots, len(lens), out, d, dtype, max(lens))
+    us = _time(fn, args.iters)
+    byts = n * (2 * g * d + h * e) * 4 + n * 2 * h * 4 + n * h * e * 4 + 2 * len(lens) * h * d * e * 4
+    flops = 4 * n * h * d * e
+    return {"kernel": f"scan/scalar/{args.form}", "heads": h, "groups": g, "key_dim": d, "value_dim": e, "rows": n,
             "requests": len(lens), "us": round(us, 2), "GBps": round(byts / us / 1e3, 1),
             "TFLOPs": round(flops / us / 1e6, 2), "us_per_token": round(us / max(lens), 4)}
 
@@ -532,7 +557,9 @@ def main(argv=None) -> int:
     a.add_argument("--iters", type=int, default=20)
     a.set_defaults(fn=attention)
     sc = sub.add_parser("scan")
-    sc.add_argument("--mode", choices=["decay", "gates"], default="gates")
+    sc.add_argument("--mode", choices=["decay", "gates", "scalar"], default="gates",
+                    help="a decay per key channel, scalar gates with a running maximum, or one decay per token and head")
+    sc.add_argument("--groups", type=int, default=0, help="scalar: groups of heads that share q and k (0: every head its own)")
     sc.add_argument("--form", choices=["decode", "prefill"], default="prefill")
     sc.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
     sc.add_argument("--batch", type=int, default=8)
