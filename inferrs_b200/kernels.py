@@ -1074,8 +1074,8 @@ def decay_scan(x: torch.Tensor, q_col: int, k_col: int, v_col: int, groups: int,
             or (skip is not None and skip.shape[0] != heads) \
             or q_start.shape[0] < n_requests + 1 or slots.shape[0] < n_requests or state[0].numel() < heads * d_dim * e_dim:
         raise KernelError(f"decay_scan: x {tuple(x.shape)}, out {tuple(out.shape)}, {groups} groups of {d_dim}")
-    if d_dim > 512:
-        raise KernelError(f"decay_scan: {d_dim} key channels per head are more than the kernel's 512")
+    if d_dim > 256:
+        raise KernelError(f"decay_scan: {d_dim} key channels per head are more than the kernel's 256")
     _check(_core(act_dtype).ib_decay_scan(
         _p(x), x.shape[1], int(q_col), int(k_col), int(v_col), int(groups), keep_p, keep_ld, take_p, take_ld, _p(skip),
         _p(state), state[0].numel(), _p(q_start), _p(slots), int(n_requests), _p(out), heads, d_dim, e_dim,

@@ -528,15 +528,18 @@ def test_the_key_just_before_a_chunk_is_not_seen_and_its_first_key_is(name, chun
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,E,per_token", [(4, 2, 20, 12, True), (1, 1, 128, 64, False), (3, 3, 36, 8, True),
-                                                (6, 2, 48, 32, True), (2, 1, 300, 33, False), (4, 4, 64, 64, False)])
-def test_decay_scan_against_the_recurrence(H, G, D, E, per_token, dtype):
+                                                (6, 2, 48, 32, True), (2, 1, 250, 33, False), (4, 4, 64, 64, False),
+                                                (16, 2, 128, 128, True)])
+@pytest.mark.parametrize("aligned", [False, True])
+def test_decay_scan_against_the_recurrence(H, G, D, E, per_token, aligned, dtype):
     """Three requests of unequal length side by side, in two steps, their state slots out of order; keys shared by
     the heads of a group; a decay per head for all tokens or one per token; key sizes that are no multiple of 16 and
     value sizes that are no multiple of 32."""
     from inferrs_b200 import kernels
     g = torch.Generator().manual_seed(H * 100 + D)
     slots = [2, 0, 1]
-    ld = 2 * G * D + H * E + 3
+    c0 = 4 if aligned else 1                                  # where q starts in a row: on a 16-byte boundary or not
+    ld = (2 * G * D + H * E + c0 + 6) // 4 * 4 + (0 if aligned else 1)
     n_state = H * D * E + 11                                  # the slot holds more than the matrices
     state = torch.zeros((4, n_state), dtype=torch.float32, device="cuda")
     S = [torch.zeros(H, D, E, dtype=torch.float64) for _ in range(3)]
@@ -550,15 +553,15 @@ def test_decay_scan_against_the_recurrence(H, G, D, E, per_token, dtype):
         gates = torch.cat([keep, take], dim=1).cuda().contiguous()
         out = torch.empty((n, H, E), dtype=torch.float32, device="cuda")
         q_start = dev([0] + list(np.cumsum(lens)))
-        kernels.decay_scan(x.cuda(), 1, 1 + G * D, 1 + 2 * G * D, G, gates[:, :H] if per_token else fixed.cuda(),
+        kernels.decay_scan(x.cuda(), c0, c0 + G * D, c0 + 2 * G * D, G, gates[:, :H] if per_token else fixed.cuda(),
                            gates[:, H:] if per_token else None, None if skip is None else skip.cuda(), state, q_start,
                            dev(slots), 3, out, D, dtype, max_rows=max(lens))
         at = 0
         for r, n_r in enumerate(lens):
             for t in range(at, at + n_r):
-                q = x[t, 1:1 + G * D].reshape(G, D).double().repeat_interleave(H // G, dim=0)
-                k = x[t, 1 + G * D:1 + 2 * G * D].reshape(G, D).double().repeat_interleave(H // G, dim=0)
-                v = x[t, 1 + 2 * G * D:1 + 2 * G * D + H * E].reshape(H, E).double()
+                q = x[t, c0:c0 + G * D].reshape(G, D).double().repeat_interleave(H // G, dim=0)
+                k = x[t, c0 + G * D:c0 + 2 * G * D].reshape(G, D).double().repeat_interleave(H // G, dim=0)
+                v = x[t, c0 + 2 * G * D:c0 + 2 * G * D + H * E].reshape(H, E).double()
                 a = keep[t].double() if per_token else fixed.double()
                 b = take[t].double() if per_token else torch.ones(H, dtype=torch.float64)
                 S[r] = a[:, None, None] * S[r] + b[:, None, None] * k[:, :, None] * v[:, None, :]
