@@ -44,10 +44,77 @@ __global__ void scaled_add_norm_kernel(float* __restrict__ residual, const act_t
     }
 }
 
+// Four elements per thread and step, the row kept in registers between the two passes: for widths that are
+// multiples of 4 and at most 4 * SAN_KEEP * (threads per block).
+#define SAN_KEEP 4
+struct alignas(sizeof(act_t) * 4) SanActVec4 { act_t v[4]; };
+
+__global__ void scaled_add_norm_vec4_kernel(float* __restrict__ residual, const act_t* __restrict__ delta, float alpha,
+                                            const float* __restrict__ weight, float eps, act_t* __restrict__ copy,
+                                            int width) {
+    __shared__ float red[32];
+    ib_grid_dependency_launch();
+    const int n4 = width >> 2;
+    float4 wk[SAN_KEEP];       // the norm's weights are fetched while the kernel before this one still runs
+#pragma unroll
+    for (int k = 0; k < SAN_KEEP; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j < n4) wk[k] = reinterpret_cast<const float4*>(weight)[j];
+    }
+    ib_grid_dependency_wait();
+    float4* res = reinterpret_cast<float4*>(residual + (size_t)blockIdx.x * width);
+    const SanActVec4* del = delta ? reinterpret_cast<const SanActVec4*>(delta + (size_t)blockIdx.x * width) : nullptr;
+    float4 keep[SAN_KEEP];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < SAN_KEEP; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j < n4) {
+            float4 v = res[j];
+            v.x *= alpha; v.y *= alpha; v.z *= alpha; v.w *= alpha;
+            if (del) {
+                const SanActVec4 d = del[j];
+                v.x += ib_to_float(d.v[0]); v.y += ib_to_float(d.v[1]);
+                v.z += ib_to_float(d.v[2]); v.w += ib_to_float(d.v[3]);
+            }
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            keep[k] = v;
+        }
+    }
+    ss = ib_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    SanActVec4* dst = copy ? reinterpret_cast<SanActVec4*>(copy + (size_t)blockIdx.x * width) : nullptr;
+#pragma unroll
+    for (int k = 0; k < SAN_KEEP; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j >= n4) break;
+        float4 v = keep[k];
+        v.x = v.x * inv * wk[k].x; v.y = v.y * inv * wk[k].y; v.z = v.z * inv * wk[k].z; v.w = v.w * inv * wk[k].w;
+        res[j] = v;
+        if (dst) {
+            SanActVec4 o;
+            o.v[0] = ib_from_float<act_t>(v.x); o.v[1] = ib_from_float<act_t>(v.y);
+            o.v[2] = ib_from_float<act_t>(v.z); o.v[3] = ib_from_float<act_t>(v.w);
+            dst[j] = o;
+        }
+    }
+}
+
+static inline bool sm_aligned16(const void* p) { return p == nullptr || ((uintptr_t)p & 15) == 0; }
+
 IB_EXPORT int ib_scaled_add_norm(float* residual, const void* delta, float alpha, const float* weight, float eps,
                                  void* copy, int n_rows, int width, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (width <= 0 || residual == nullptr || weight == nullptr) return IB_ERR_ARGUMENT;
+    if ((width & 3) == 0 && width <= 4 * SAN_KEEP * 1024 && sm_aligned16(residual) && sm_aligned16(delta) &&
+        sm_aligned16(weight) && sm_aligned16(copy)) {
+        int t4 = 64;   // enough threads that SAN_KEEP float4 per thread hold the row
+        while (4 * SAN_KEEP * t4 < width) t4 <<= 1;
+        if (width >= 1024 && 4 * t4 < width && t4 < 256) t4 = 256;
+        ib_launch(scaled_add_norm_vec4_kernel, n_rows, t4, 0, stream, residual, (const act_t*)delta, alpha, weight, eps,
+                  (act_t*)copy, width);
+        return ib_launch_status();
+    }
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     ib_launch(scaled_add_norm_kernel, n_rows, threads, 0, stream, residual, (const act_t*)delta, alpha, weight, eps,
               (act_t*)copy, width);
@@ -70,28 +137,26 @@ __global__ void heads_to_float_kernel(const act_t* __restrict__ src, long ld, He
                                       const float* __restrict__ sin_table, int rot_dim, int table_rows,
                                       const int* __restrict__ positions) {
     ib_grid_dependency_sync();
-    const int row = blockIdx.x;
+    const int row = blockIdx.y;
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;     // a number of the row's slices, counted through all of them
+    int s = 0;
+    while (s < P.n && idx >= P.n_heads[s] * P.dim[s]) { idx -= P.n_heads[s] * P.dim[s]; ++s; }
+    if (s >= P.n) return;
     const act_t* in = src + (long)row * ld;
-    float* out = dst + (long)row * dst_ld;
     const int half = rot_dim / 2;
-    int pos = positions ? positions[row] : 0;
-    if (pos < 0) pos = 0;
-    if (pos >= table_rows) pos = table_rows - 1;     // the host sizes the tables for every position of the model
-    for (int s = 0; s < P.n; ++s) {
-        const int d = P.dim[s], total = P.n_heads[s] * d;
-        const float scale = P.scale[s];
-        for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-            const int j = idx % d;
-            const act_t* h = in + P.src_col[s] + (idx - j);
-            float v = ib_to_float(h[j]);
-            if (P.rotate[s] && j < rot_dim) {
-                const int i = j < half ? j : j - half;
-                const float c = cos_table[(long)pos * half + i], sn = sin_table[(long)pos * half + i];
-                v = j < half ? v * c - ib_to_float(h[j + half]) * sn : v * c + ib_to_float(h[j - half]) * sn;
-            }
-            out[P.dst_col[s] + idx] = v * scale;
-        }
+    const int d = P.dim[s];
+    const int j = idx % d;
+    const act_t* h = in + P.src_col[s] + (idx - j);
+    float v = ib_to_float(h[j]);
+    if (P.rotate[s] && j < rot_dim) {
+        int pos = positions[row];
+        if (pos < 0) pos = 0;
+        if (pos >= table_rows) pos = table_rows - 1;     // the host sizes the tables for every position of the model
+        const int i = j < half ? j : j - half;
+        const float c = cos_table[(long)pos * half + i], sn = sin_table[(long)pos * half + i];
+        v = j < half ? v * c - ib_to_float(h[j + half]) * sn : v * c + ib_to_float(h[j - half]) * sn;
     }
+    dst[(long)row * dst_ld + P.dst_col[s] + idx] = v * P.scale[s];
 }
 
 IB_EXPORT int ib_heads_to_float(const void* src, long ld, int n_slices, const int* src_col, const int* dst_col,
@@ -103,7 +168,7 @@ IB_EXPORT int ib_heads_to_float(const void* src, long ld, int n_slices, const in
         return IB_ERR_ARGUMENT;
     HeadSlices P;
     P.n = n_slices;
-    int widest = 0;
+    int total = 0;
     for (int s = 0; s < n_slices; ++s) {
         P.src_col[s] = src_col[s]; P.dst_col[s] = dst_col[s]; P.n_heads[s] = n_heads[s]; P.dim[s] = dim[s];
         P.rotate[s] = rotate[s]; P.scale[s] = scale[s];
@@ -111,11 +176,12 @@ IB_EXPORT int ib_heads_to_float(const void* src, long ld, int n_slices, const in
         if (rotate[s] && rot_dim > 0 && (cos_table == nullptr || sin_table == nullptr || positions == nullptr ||
                                         table_rows <= 0))
             return IB_ERR_ARGUMENT;
-        if (n_heads[s] * dim[s] > widest) widest = n_heads[s] * dim[s];
+        total += n_heads[s] * dim[s];
     }
-    const int threads = widest >= 1024 ? 256 : 128;
-    ib_launch(heads_to_float_kernel, n_rows, threads, 0, stream, (const act_t*)src, ld, P, dst, dst_ld, cos_table,
-              sin_table, rot_dim, table_rows, positions);
+    if (n_rows > 65535) return IB_ERR_UNSUPPORTED;
+    const int threads = 256;
+    ib_launch(heads_to_float_kernel, dim3((total + threads - 1) / threads, n_rows), threads, 0, stream,
+              (const act_t*)src, ld, P, dst, dst_ld, cos_table, sin_table, rot_dim, table_rows, positions);
     return ib_launch_status();
 }
 
@@ -215,21 +281,34 @@ IB_EXPORT int ib_conv_state_shift(const void* proj, long ld, int conv_col, int C
 // ---------------------------------------------------------------------------
 __global__ void gate_group_norm_kernel(const float* __restrict__ y, const act_t* __restrict__ z, long z_ld,
                                        const float* __restrict__ weight, int groups, int part, float eps,
-                                       act_t* __restrict__ out) {
+                                       act_t* __restrict__ out, int warps_per_part) {
+    __shared__ float sums[32];
     ib_grid_dependency_sync();
     const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const long inner = (long)groups * part;
-    for (int g = warp; g < groups; g += n_warps) {
+    // few parts: every part has `warps_per_part` warps of the block (one round); many parts: a warp each, in rounds
+    const int parts_per_round = n_warps / warps_per_part;
+    const int sub = warp % warps_per_part, lanes = 32 * warps_per_part;
+    for (int g0 = 0; g0 < groups; g0 += parts_per_round) {
+        const int g = g0 + warp / warps_per_part;
+        const bool mine = g < groups && warp / warps_per_part < parts_per_round;
         const float* yr = y + (long)row * inner + (long)g * part;
         const act_t* zr = z + (long)row * z_ld + (long)g * part;
         float ss = 0.0f;
-        for (int j = lane; j < part; j += 32) {
-            const float v = yr[j] * sm_silu(ib_to_float(zr[j]));
-            ss += v * v;
-        }
+        if (mine)
+            for (int j = sub * 32 + lane; j < part; j += lanes) {
+                const float v = yr[j] * sm_silu(ib_to_float(zr[j]));
+                ss += v * v;
+            }
         ss = ib_warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)part + eps);
-        for (int j = lane; j < part; j += 32) {
+        __syncthreads();                     // `sums` may still be read from the round before
+        if (lane == 0) sums[warp] = ss;
+        __syncthreads();
+        if (!mine) continue;
+        float total = 0.0f;
+        for (int w = 0; w < warps_per_part; ++w) total += sums[(warp / warps_per_part) * warps_per_part + w];
+        const float inv = 1.0f / sqrtf(total / (float)part + eps);
+        for (int j = sub * 32 + lane; j < part; j += lanes) {
             const float v = yr[j] * sm_silu(ib_to_float(zr[j]));
             out[(long)row * inner + (long)g * part + j] = ib_from_float<act_t>(v * inv * weight[(long)g * part + j]);
         }
@@ -241,9 +320,14 @@ IB_EXPORT int ib_gate_group_norm(const float* y, const void* z, long z_ld, const
     if (n_rows <= 0) return IB_OK;
     if (groups <= 0 || inner <= 0 || inner % groups || y == nullptr || z == nullptr || weight == nullptr)
         return IB_ERR_ARGUMENT;
-    const int warps = groups < 8 ? groups : 8;
-    ib_launch(gate_group_norm_kernel, n_rows, 32 * warps, 0, stream, y, (const act_t*)z, z_ld, weight, groups,
-              inner / groups, eps, (act_t*)out);
+    const int part = inner / groups;
+    int warps = 8;
+    while (warps > 1 && warps * 32 > inner) warps >>= 1;          // a narrow row needs no eight warps
+    int per_part = warps / groups;                                 // warps that share one part
+    if (per_part < 1) per_part = 1;
+    while (per_part > 1 && per_part * 32 > part) per_part >>= 1;
+    ib_launch(gate_group_norm_kernel, n_rows, 32 * warps, 0, stream, y, (const act_t*)z, z_ld, weight, groups, part, eps,
+              (act_t*)out, per_part);
     return ib_launch_status();
 }
 
@@ -263,10 +347,43 @@ __global__ void clamped_gate_kernel(const act_t* __restrict__ gate_up, act_t* __
     }
 }
 
+// Sixteen bytes per thread (eight bfloat16 or four float) and one row per blockIdx.y, so that no thread divides to
+// find its row: for inner sizes that are multiples of that many elements.
+#define SM_VEC (16 / (int)sizeof(act_t))
+struct alignas(16) SmActVec { act_t v[SM_VEC]; };
+
+__global__ void clamped_gate_vec_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner,
+                                        float limit, float slope) {
+    ib_grid_dependency_sync();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= inner / SM_VEC) return;
+    const long r = blockIdx.y;
+    const SmActVec g = reinterpret_cast<const SmActVec*>(gate_up + r * 2 * inner)[j];
+    const SmActVec u = reinterpret_cast<const SmActVec*>(gate_up + r * 2 * inner + inner)[j];
+    SmActVec o;
+#pragma unroll
+    for (int k = 0; k < SM_VEC; ++k) {
+        const float gv = fminf(ib_to_float(g.v[k]), limit);
+        const float uv = fminf(fmaxf(ib_to_float(u.v[k]), -limit), limit);
+        o.v[k] = ib_from_float<act_t>(gv * sm_sigmoid(slope * gv) * (uv + 1.0f));
+    }
+    reinterpret_cast<SmActVec*>(out + r * inner)[j] = o;
+}
+
 IB_EXPORT int ib_clamped_gate(const void* gate_up, void* out, int n_rows, int inner, float limit, float slope,
                               cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (inner <= 0 || !(limit > 0.0f)) return IB_ERR_ARGUMENT;
+    if (inner % SM_VEC == 0 && sm_aligned16(gate_up) && sm_aligned16(out)) {
+        const int nv = inner / SM_VEC;
+        const int threads = nv >= 256 ? 256 : ((nv + 31) / 32) * 32;
+        for (int r0 = 0; r0 < n_rows; r0 += 65535) {   // blockIdx.y holds at most 65,535 rows
+            const int rows = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
+            ib_launch(clamped_gate_vec_kernel, dim3((nv + threads - 1) / threads, rows), threads, 0, stream,
+                      (const act_t*)gate_up + (long)r0 * 2 * inner, (act_t*)out + (long)r0 * inner, inner, limit, slope);
+        }
+        return ib_launch_status();
+    }
     const long total = (long)n_rows * inner;
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;
@@ -353,12 +470,49 @@ __global__ void routed_gate_kernel(const act_t* __restrict__ gate_up, const floa
     }
 }
 
+// The same, sixteen bytes per thread and one row per blockIdx.y: for expert sizes that are multiples of that many
+// elements (a thread's elements then belong to one expert).  The columns of an expert that the token did not
+// choose are not read.
+__global__ void routed_gate_vec_kernel(const act_t* __restrict__ gate_up, const float* __restrict__ weights,
+                                       int n_weights, int n_experts, int ff, act_t* __restrict__ out, int inner) {
+    ib_grid_dependency_sync();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= inner / SM_VEC) return;
+    const long r = blockIdx.y;
+    int e = (j * SM_VEC) / ff;
+    if (e > n_experts) e = n_experts;
+    const float wt = weights[r * n_weights + e];
+    SmActVec o;
+    if (wt != 0.0f) {
+        const SmActVec g = reinterpret_cast<const SmActVec*>(gate_up + r * 2 * inner)[j];
+        const SmActVec u = reinterpret_cast<const SmActVec*>(gate_up + r * 2 * inner + inner)[j];
+#pragma unroll
+        for (int k = 0; k < SM_VEC; ++k)
+            o.v[k] = ib_from_float<act_t>(sm_silu(ib_to_float(g.v[k])) * ib_to_float(u.v[k]) * wt);
+    } else {
+#pragma unroll
+        for (int k = 0; k < SM_VEC; ++k) o.v[k] = ib_from_float<act_t>(0.0f);
+    }
+    reinterpret_cast<SmActVec*>(out + r * inner)[j] = o;
+}
+
 IB_EXPORT int ib_routed_gate(const void* gate_up, const float* weights, int n_weights, int n_experts, int ff, void* out,
                              int n_rows, int inner, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (inner <= 0 || ff <= 0 || n_experts <= 0 || (long)n_experts * ff > inner || weights == nullptr ||
         n_weights < n_experts + ((long)n_experts * ff < inner ? 1 : 0))
         return IB_ERR_ARGUMENT;
+    if (ff % SM_VEC == 0 && inner % SM_VEC == 0 && sm_aligned16(gate_up) && sm_aligned16(out)) {
+        const int nv = inner / SM_VEC;
+        const int threads = nv >= 256 ? 256 : ((nv + 31) / 32) * 32;
+        for (int r0 = 0; r0 < n_rows; r0 += 65535) {   // blockIdx.y holds at most 65,535 rows
+            const int rows = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
+            ib_launch(routed_gate_vec_kernel, dim3((nv + threads - 1) / threads, rows), threads, 0, stream,
+                      (const act_t*)gate_up + (long)r0 * 2 * inner, weights + (long)r0 * n_weights, n_weights, n_experts,
+                      ff, (act_t*)out + (long)r0 * inner, inner);
+        }
+        return ib_launch_status();
+    }
     const long total = (long)n_rows * inner;
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;

@@ -627,7 +627,7 @@ def test_convolution_with_its_state_and_the_gates(taps, C, H, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("groups,inner", [(1, 48), (2, 192), (3, 45), (12, 96)])
+@pytest.mark.parametrize("groups,inner", [(1, 48), (2, 192), (3, 45), (12, 96), (2, 2048), (1, 4096), (16, 1024)])
 def test_gate_then_norm_in_parts(groups, inner, dtype):
     from inferrs_b200 import kernels
     g = torch.Generator().manual_seed(inner)
@@ -644,25 +644,27 @@ def test_gate_then_norm_in_parts(groups, inner, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_clamped_gate(dtype):
+@pytest.mark.parametrize("inner", [37, 64, 1000])
+def test_clamped_gate(inner, dtype):
     from inferrs_b200 import kernels
     g = torch.Generator().manual_seed(8)
-    gu = (torch.randn(5, 2 * 37, generator=g) * 3).to(dtype)
+    gu = (torch.randn(5, 2 * inner, generator=g) * 3).to(dtype)
     lim = 1.5
-    gg = torch.clamp(gu.double()[:, :37], max=lim)
-    uu = torch.clamp(gu.double()[:, 37:], min=-lim, max=lim)
+    gg = torch.clamp(gu.double()[:, :inner], max=lim)
+    uu = torch.clamp(gu.double()[:, inner:], min=-lim, max=lim)
     want = gg * torch.sigmoid(1.702 * gg) * (uu + 1)
-    out = torch.empty((5, 37), dtype=dtype, device="cuda")
+    out = torch.empty((5, inner), dtype=dtype, device="cuda")
     kernels.clamped_gate(gu.cuda(), out, lim, 1.702)
     assert rel_err(out, want) < (1e-5 if dtype == torch.float32 else 1e-2)
-    assert float(gu.float().max()) > lim and float(gu.float()[:, 37:].min()) < -lim     # the clamps were at work
+    assert float(gu.float().max()) > lim and float(gu.float()[:, inner:].min()) < -lim     # the clamps were at work
 
 
+@pytest.mark.parametrize("ff,shared_ff", [(6, 10), (8, 24)])
 @pytest.mark.parametrize("experts,top,shared", [(8, 4, True), (5, 2, False), (3, 3, True), (70, 6, False), (4, 1, True)])
-def test_router_weights_and_the_routed_gate(experts, top, shared):
+def test_router_weights_and_the_routed_gate(experts, top, shared, ff, shared_ff):
     from inferrs_b200 import kernels
     g = torch.Generator().manual_seed(experts)
-    n, ff, shared_ff = 9, 6, 10
+    n = 9
     logits = torch.randn(n, experts + int(shared) + 2, generator=g) * 2
     logits[0, 1] = logits[0, 0]                                   # equal logits: the lower index wins
     bias = torch.randn(experts, generator=g)
