@@ -77,7 +77,11 @@ def _rotate(x, cos, sin, rot_dim, interleaved=False):
 
 
 def qk_norm_rope_store(qkv, n_heads, n_kv_heads, head_dim, store_kv, q_weight, k_weight, eps, cos, sin, rot_dim,
-                       positions, row_request, block_table, k_pages, v_pages, q_out, interleaved=False):
+                       positions, row_request, block_table, k_pages, v_pages, q_out, interleaved=False, norm_q=None,
+                       norm_k=None, norm_after_rotation=False):
+    # the plain order only (norm, then rotation; a normed kind has its weight; values as large as keys)
+    assert not norm_after_rotation and norm_q in (None, q_weight is not None) and \
+        norm_k in (None, k_weight is not None and store_kv, k_weight is not None)
     n = qkv.shape[0]
     d = head_dim
     x = qkv.float()
@@ -116,7 +120,7 @@ def paged_attention_generic(q, k_pages, v_pages, block_table, row_request, posit
     for r in range(n):
         pos = int(positions[r])
         req = int(row_request[r])
-        lo = max(0, pos - window + 1) if window else 0
+        lo = (max(0, pos - window + 1) if window > 0 else (pos // -window) * -window) if window else 0
         js = torch.arange(lo, pos + 1)
         pages = block_table[req, (js // page_size).long()].long()
         assert (pages >= 0).all(), "a visible key lies in a page that was given back"

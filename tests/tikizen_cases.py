@@ -60,7 +60,7 @@ CASE_Q = {
     "layers": [
         {"type": "mamba2", "mixer": {"heads": 2, "vdim": 30, "state": 16, "groups": 1, "conv": 1, "norm_groups": 1},
          "mlp": _moe(20, 4, 1)},
-        {"type": "retention", "mixer": {"heads": 1, "dim": 16, "vdim": 64, "decay": [0.98], "rot": _rot(100.0, 16)},
+        {"type": "retention", "mixer": {"heads": 1, "dim": 16, "vdim": 64, "decay": [0.98]},      # no rotation
          "mlp": _dense(48, 0.7)},
         {"type": "mamba2", "mixer": {"heads": 3, "vdim": 8, "state": 36, "groups": 3, "conv": 2, "norm_groups": 2},
          "mlp": None},
