@@ -321,6 +321,64 @@ def test_a_marked_token_is_seen_inside_its_chunk_and_nowhere_else(dim, dtype):
         assert all(abs(float(g[p, 63])) < 0.5 for p, seen in probes.items() if not seen)
 
 
+ONE_RETENTION = {
+    "architecture": "Tikizen", "vocab": 64, "width": 64, "norm": {"eps": 1e-5}, "postln_alpha": 1.0,
+    "layers": [{"type": "retention", "mlp": None,
+                "mixer": {"heads": 1, "dim": 32, "vdim": 32, "decay": [1.0]}}],
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("decay", [1.0, 0.99])
+def test_a_marked_token_far_back_is_kept_by_the_state(decay, dtype):
+    """One layer of retention without rotation whose keys are the tokens' ids; the query of token 7 asks for token 9,
+    and only token 9 has a value: the mark.  Token 9 stands once, at position 5 of a prompt of 400 tokens.  Every
+    token 7 after it returns the mark, hundreds of tokens later too (the head is brought to unit size, so a decay
+    only weakens what the norm then restores); a token 7 before it does not, and neither does a token 7 early in the
+    next request that takes the same state slot."""
+    case = json.loads(json.dumps(ONE_RETENTION))
+    case["layers"][0]["mixer"]["decay"] = [decay]
+    w = make_weights(case, 2)
+    width, vocab, dim = 64, 64, 32
+    w["embed"], w["embed.norm"] = torch.eye(vocab, width) * 8.0, torch.ones(width)
+    pick = torch.eye(width)[:dim].clone()
+    ask = pick.clone()
+    ask[7, 7], ask[9, 7] = 0.0, 1.0                               # token 7 asks for token 9
+    w["l0.mix.q"], w["l0.mix.k"] = ask, pick
+    v = torch.zeros(dim, width)
+    v[0, 9] = 4.0                                                 # only token 9 has a value
+    w["l0.mix.v"] = v
+    w["l0.mix.g"] = torch.full((dim, width), 0.25)                # the same gate for every token
+    o = torch.zeros(width, dim)
+    o[63, 0] = 50.0                                               # the mark goes to channel 63 of the stream
+    w["l0.mix.o"] = o
+    w["l0.norm1"], w["final.norm"] = torch.ones(width), torch.ones(width)
+    w["head"] = torch.eye(vocab, width)
+    n, marked_at = 400, 5
+    toks = [(11 + i % 20) for i in range(n)]
+    toks[marked_at] = 9
+    probes = {2: False, 6: True, 17: True, 64: True, 250: True, 399: True}
+    for p in probes:
+        toks[p] = 7
+    want = pt.forward(case, w, toks)
+    assert {p: bool(want[p, 63] > 4.0) for p in probes} == probes
+    runner = make_runner(case, w, dtype, n_pages=60, max_requests=1)      # one slot: the next request takes it again
+    runner.admit("w")
+    got = runner.step([entry("w", toks)])
+    runner.release("w")
+    runner.admit("c")
+    rows, at = [], 0
+    for k in cut(300, [3, 2, 1, 64, 30, 2, 90]):                  # the mark and the first probes in portions of their own
+        rows.append(runner.step([entry("c", toks[at:at + k])]))
+        at += k
+    for t in toks[300:]:
+        rows.append(runner.step([entry("c", [t])]))
+    for g in (got, torch.cat(rows)):
+        assert_close(g, want, dtype)
+        assert {p: bool(g[p, 63] > 4.0) for p in probes} == probes
+        assert abs(float(g[2, 63])) < 0.5
+
+
 # ---------------------------------------------------------------------------------------------------
 # kernels alone
 # ---------------------------------------------------------------------------------------------------
