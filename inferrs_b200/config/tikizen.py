@@ -11,7 +11,7 @@ config.json gives every size and every constant that differs between models of t
     max_positions  optional: the most positions of a sequence (rotation tables are made for that many)
 
 Mixers: "attention" (heads, kv_heads, dim, vdim, scale, rot {base, dims, scaling {factor, original, fast, slow}},
-mask {size}, kv_from), "retention" (heads, dim, vdim, decay [per head], rot {base, dims}), "mamba2" (heads, vdim,
+mask {size}, kv_from), "retention" (heads, dim, vdim, decay [per head], rot as above), "mamba2" (heads, vdim,
 state, groups, conv, norm_groups).  Feed-forwards: {"kind": "dense", "ff", "limit"} and {"kind": "moe", "expert":
 {"ff"}, "router": {"experts", "top"}, "shared": {"ff"}}.
 
@@ -136,7 +136,7 @@ class TikizenConfig:
         return TikizenConfig(**{**self.__dict__, "layers": tuple(layers)})
 
 
-def _check_rot(src: str, where: str, rot, key_dim: int, scaling_allowed: bool):
+def _check_rot(src: str, where: str, rot, key_dim: int):
     if rot is None:
         return
     if not isinstance(rot, dict) or set(rot) - _ROT_KEYS or not {"base", "dims"} <= set(rot):
@@ -148,9 +148,8 @@ def _check_rot(src: str, where: str, rot, key_dim: int, scaling_allowed: bool):
                           f"above 1; got {dims}, {base}")
     sc = rot.get("scaling")
     if sc is not None:
-        if not scaling_allowed or not isinstance(sc, dict) or set(sc) != _SCALING_KEYS:
-            raise ConfigError(f"{src}: {where}.rot.scaling must be an object with {sorted(_SCALING_KEYS)} (attention "
-                              f"layers only), got {sc!r}")
+        if not isinstance(sc, dict) or set(sc) != _SCALING_KEYS:
+            raise ConfigError(f"{src}: {where}.rot.scaling must be an object with {sorted(_SCALING_KEYS)}, got {sc!r}")
         for k in _SCALING_KEYS:
             if not _number(src, f"{where}.rot.scaling.{k}", sc[k], float) > 0:
                 raise ConfigError(f"{src}: {where}.rot.scaling.{k} must be positive, got {sc[k]!r}")
@@ -171,7 +170,7 @@ def _check_mixer(src: str, where: str, kind: str, given: Dict[str, Any], layers,
         if out["heads"] % out["kv_heads"]:
             raise ConfigError(f"{src}: {where}.mixer: {out['heads']} heads are not a multiple of {out['kv_heads']} "
                               f"kv_heads")
-        _check_rot(src, f"{where}.mixer", out.get("rot"), out["dim"], True)
+        _check_rot(src, f"{where}.mixer", out.get("rot"), out["dim"])
         mask = out.get("mask")
         if mask is not None and (not isinstance(mask, dict) or set(mask) != {"size"}
                                  or _number(src, f"{where}.mixer.mask.size", mask["size"], int) <= 0):
@@ -188,7 +187,7 @@ def _check_mixer(src: str, where: str, kind: str, given: Dict[str, Any], layers,
         if not isinstance(decay, list) or len(decay) != out["heads"] \
                 or any(not 0 < _number(src, f"{where}.mixer.decay", a, float) <= 1 for a in decay):
             raise ConfigError(f"{src}: {where}.mixer.decay must list one decay in (0, 1] per head, got {decay!r}")
-        _check_rot(src, f"{where}.mixer", out.get("rot"), out["dim"], False)
+        _check_rot(src, f"{where}.mixer", out.get("rot"), out["dim"])
     else:
         if out["heads"] % out["groups"] or (out["heads"] * out["vdim"]) % out["norm_groups"]:
             raise ConfigError(f"{src}: {where}.mixer: heads must divide into groups and heads * vdim into norm_groups")

@@ -55,6 +55,7 @@ def test_a_second_norm_without_a_feed_forward_is_read_from_the_tensor_names():
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=26), "rot"),
     (lambda c: c["layers"][3]["mixer"].update(decay=[0.5, 0.5]), "decay"),
     (lambda c: c["layers"][3]["mixer"]["rot"].update(scaling={"factor": 2.0}), "scaling"),
+    (lambda c: c["layers"][0]["mixer"]["rot"]["scaling"].update(slow=0.0), "scaling"),
     (lambda c: c["layers"][1]["mixer"].update(groups=3), "groups"),
     (lambda c: c["layers"][0].update(mlp={"kind": "dense", "ff": 8}), "dense"),
     (lambda c: c["layers"][1]["mlp"]["router"].update(top=9), "top"),
