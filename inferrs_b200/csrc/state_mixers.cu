@@ -276,7 +276,7 @@ IB_EXPORT int ib_conv_state_shift(const void* proj, long ld, int conv_col, int C
 }
 
 // ---------------------------------------------------------------------------
-// out[r, :] = norm_in_groups(y[r, :] * silu(z[r, :])) * weight: the gate comes before the norm; each of `groups`
+// out[r, :] = norm_in_groups(y[r, :] * silu(z[r, :])) * weight (gated first, normed second); each of `groups`
 // equal consecutive parts of the row is divided by its own root mean square.  One warp per part.
 // ---------------------------------------------------------------------------
 __global__ void gate_group_norm_kernel(const float* __restrict__ y, const act_t* __restrict__ z, long z_ld,

@@ -974,7 +974,7 @@ def conv_state_shift(proj: torch.Tensor, conv_col: int, channels: int, taps: int
 
 def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out: torch.Tensor):
     """out = (y * silu(z)) with each of ``groups`` equal consecutive parts of the row divided by its root mean square,
-    times ``weight``: the gate comes before the norm.  ``y`` float32 [rows, inner]; ``z`` a [rows, inner] view of a
+    times ``weight`` (gated first, normed second).  ``y`` float32 [rows, inner]; ``z`` a [rows, inner] view of a
     wider projection in the activation dtype."""
     act = out.dtype
     _need(y, "y", (torch.float32,), 2)

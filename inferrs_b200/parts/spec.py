@@ -118,7 +118,7 @@ class RoutedExpertsSpec:
     experts with the largest logits are chosen and weighed by the softmax over the chosen logits alone; the output is
     the weighted sum of down_e( silu(gate_e(x)) * up_e(x) ) over the chosen.  ``experts`` names every expert's
     (gate, up, down) tensors.  ``shared`` (optional, (gate, up, down, gate vector) with ``shared_inner``): an expert
-    that runs for every token and is added times sigmoid(gate_vector . x)."""
+    that every token uses; its output is added times sigmoid(gate_vector . x)."""
 
     width: int
     inner: int
@@ -133,7 +133,7 @@ class RoutedExpertsSpec:
 
 @dataclass(frozen=True)
 class FixedDecayScanSpec:
-    """Retention: linear attention with a fixed decay per head and neither softmax nor denominator.  Per head a
+    """Retention: linear attention whose state fades by a fixed factor per head; the scores go through no softmax and no normaliser.  Per head a
     matrix state S [key_dim, value_dim], S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t; q and k are rotated by
     position (``position``), k is then multiplied by key_dim^(-1/2); each head's o is divided by its root mean square
     (no weight); the heads times silu(gate(x)) go through ``o_proj``."""
@@ -155,13 +155,14 @@ class FixedDecayScanSpec:
 
 @dataclass(frozen=True)
 class StateSpaceScanSpec:
-    """The state-space mixer of Mamba-2.  ``in_proj`` gives [z: inner | x: inner | B: groups*state | C: groups*state |
-    dt: n_heads] with inner = n_heads * value_dim.  x, B and C pass a causal convolution per channel (``conv``
-    [channels, taps] with ``conv_bias``; the last tap is the current token's) and silu; dt = softplus(dt + dt_bias).
-    Per head (head h reads group h / (n_heads / groups)) a state S [state, value_dim]:
-    S_t = exp(-exp(a_log_h) dt) S_{t-1} + dt B_t x_t^T, y_t = S_t^T C_t + skip_h x_t.  y times silu(z) is divided by
-    its root mean square in ``norm_groups`` equal parts, multiplied by ``out_norm`` and goes through ``o_proj``.  The
-    last taps - 1 inputs of the convolution are part of the state."""
+    """The state-space mixer of Mamba-2.  The columns of ``in_proj``'s output are, in order: the gate z (inner), x
+    (inner), B (groups * state), C (groups * state) and dt (n_heads), with inner = n_heads * value_dim.  x, B and C
+    go through a causal convolution per channel over the last ``taps`` inputs (``conv`` [channels, taps], the last tap
+    weighing the token itself, plus ``conv_bias``) and silu; dt = softplus(dt + dt_bias).  Per head (head h reads
+    group h / (n_heads / groups) of B and C) a state S [state, value_dim]:
+    S_t = exp(-exp(a_log_h) dt) S_{t-1} + dt B_t x_t^T, y_t = S_t^T C_t + skip_h x_t.  y silu(z) is divided by its
+    root mean square in ``norm_groups`` equal parts (gated first, normed second), multiplied by ``out_norm`` and goes
+    through ``o_proj``.  The convolution's last taps - 1 inputs belong to the per-request state."""
 
     width: int
     n_heads: int

@@ -124,7 +124,7 @@ def mamba2(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float) -> torch.
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
     padded = torch.cat([torch.zeros(taps - 1, xbc.shape[1], dtype=h.dtype), xbc], dim=0)
     conv = w[f"{p}.conv.b"][None, :].clone().expand(T, -1).clone()
-    for j in range(taps):        # tap j looks taps - 1 - j tokens back; the last column is the current token's
+    for j in range(taps):        # tap j weighs the input taps - 1 - j tokens back, so the last tap weighs the token itself
         conv = conv + padded[j:j + T] * w[f"{p}.conv"][:, j][None, :]
     conv = silu(conv)
     x = conv[:, :inner].view(T, H, E)
